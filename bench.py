@@ -1,0 +1,449 @@
+#!/usr/bin/env python
+"""Benchmark of the quantization hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line.  The default workload is the INT8 per-channel quantize + dequantize of a
+bf16 8192 x 8192 weight (the configuration the GB/s metric is quoted on); a *step* is one
+quantize plus one dequantize of that tensor.  ``value`` is algorithmic GB/s with inputs resident
+in HBM, ``e2e`` the same through the public API from pinned host buffers, ``roofline`` the
+dominant kernel against the measured HBM peak, ``cpu_baseline`` the PyTorch CPU formulation on
+this host's cores.  With N > 1 (one process per GPU under torch.distributed.run) every rank
+runs the same per-GPU workload on its own rows (weak scaling, no data-path collective) and the
+time is the max over ranks.  ``--impl reference`` times the CPU formulation instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+# dram bytes (read + write) of one launch of the dominant kernel from an ncu capture of this
+# workload; None until a capture has been taken (summaries under profiles/).
+NCU_TRAFFIC_BYTES = {"int8_channel": None, "fp8_tensor": None, "int8_group": None}
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------
+# clocks sampler (NVML, read-only)
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.seen, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.seen.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.seen), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------
+# workloads: each returns an object with .step(i), .step_e2e(i), algorithmic bytes, etc.
+# --------------------------------------------------------------------------------------
+class Int8ChannelWorkload:
+    """INT8 symmetric per-channel (axis 0) quantize + dequantize of a bf16 [rows, cols] weight."""
+
+    name = "int8_channel"
+    dtype = "int8"
+    dominant = "quant_segments_kernel (one-pass per-channel INT8 quantize)"
+
+    def __init__(self, device, rows=8192, cols=8192, sets=3):
+        from cublade_b200 import workloads as W
+
+        self.rows, self.cols, self.sets = rows, cols, sets
+        x_host = W.int8_channel_case(rows, cols)
+        self._host_buffers(x_host, device, sets)
+        self.n = rows * cols
+        self.q_bytes = self.n * 3 + rows * 4  # 2 B read + 1 B write per element, 4 B scale per row
+        self.dq_bytes = self.n * 3 + rows * 4
+        self.bytes_per_step = self.q_bytes + self.dq_bytes
+        self.device = device
+        self.qt = [None] * sets
+        self.launches_per_step = 2
+        self.kernel_ms = []  # (quant_ms, dequant_ms) per timed step
+
+    def _host_buffers(self, x_host, device, sets):
+        # device=None builds the host input only (CPU reference arm).  Rotating buffer sets: the
+        # footprint (sets * 5 B/elem) exceeds 2 x L2, so no launch finds its input in L2.
+        if device is None:
+            self.x_host, self.y_host, self.x = x_host, None, []
+            return
+        self.x_host = x_host.pin_memory()
+        self.y_host = torch.empty_like(x_host).pin_memory()
+        self.x = [x_host.to(device) for _ in range(sets)]
+
+    def config(self):
+        return {"workload": f"int8_per_channel_axis0_quant+dequant bf16 {self.rows}x{self.cols}",
+                "bytes_per_step": self.bytes_per_step,
+                "l2_policy": f"rotating {self.sets} buffer sets ({self.sets * self.n * 5 / 1e6:.0f} MB footprint > 2x L2); "
+                             "dequantize reads codes written two steps earlier",
+                "seed": 1}
+
+    def prime(self):
+        import cublade_b200 as cb
+
+        for i in range(self.sets):
+            self.qt[i] = cb.quantize_tensor(self.x[i], dtype=torch.int8, mode="channel", ch_axis=0)
+        torch.cuda.synchronize()
+
+    def step(self, i, events=None):
+        import cublade_b200 as cb
+
+        a, b = i % self.sets, (i + 1) % self.sets
+        if events:
+            events[0].record()
+        self.qt[a] = cb.quantize_tensor(self.x[a], dtype=torch.int8, mode="channel", ch_axis=0)
+        if events:
+            events[1].record()
+        y = cb.dequantize_tensor(self.qt[b])
+        if events:
+            events[2].record()
+        return y
+
+    def step_e2e(self, i):
+        import cublade_b200 as cb
+
+        x = self.x_host.to(self.device, non_blocking=True)
+        qt = cb.quantize_tensor(x, dtype=torch.int8, mode="channel", ch_axis=0)
+        y = cb.dequantize_tensor(qt)
+        self.y_host.copy_(y, non_blocking=True)
+        return y
+
+    e2e_h2d = property(lambda self: self.n * 2)
+    e2e_d2h = property(lambda self: self.n * 2)
+
+    # CPU formulation of the same step (oracle = checker / baseline only)
+    def cpu_step(self, x_cpu):
+        from oracle import oracle as O
+
+        q, s = O.int8_quantize_channel(x_cpu)
+        return O.int8_dequantize_rows(q, s, torch.bfloat16)
+
+    def cpu_input(self):
+        return self.x_host
+
+
+class Fp8TensorWorkload(Int8ChannelWorkload):
+    """Per-tensor FP8 E4M3 quantize + dequantize of a bf16 [rows, cols] tensor with 16 outliers."""
+
+    name = "fp8_tensor"
+    dtype = "e4m3"
+    dominant = "cast_tensor_kernel (per-tensor FP8 cast, second pass)"
+
+    def __init__(self, device, rows=4096, cols=4096, sets=12):
+        from cublade_b200 import workloads as W
+
+        self.rows, self.cols, self.sets = rows, cols, sets
+        x_host = W.fp8_tensor_case(rows, cols)
+        self._host_buffers(x_host, device, sets)
+        self.n = rows * cols
+        self.q_bytes = self.n * 3 + 4  # the tensor fits in L2: the second read of x is not HBM traffic
+        self.dq_bytes = self.n * 3 + 4
+        self.bytes_per_step = self.q_bytes + self.dq_bytes
+        self.device = device
+        self.qt = [None] * sets
+        self.launches_per_step = 3
+        self.kernel_ms = []
+
+    def config(self):
+        c = super().config()
+        c["workload"] = f"fp8_e4m3_per_tensor_quant+dequant bf16 {self.rows}x{self.cols} (16 outliers of 300)"
+        c["seed"] = 0
+        return c
+
+    def _q(self, x):
+        import cublade_b200 as cb
+
+        return cb.quantize_tensor(x, dtype=torch.float8_e4m3fn, mode="tensor")
+
+    def prime(self):
+        for i in range(self.sets):
+            self.qt[i] = self._q(self.x[i])
+        torch.cuda.synchronize()
+
+    def step(self, i, events=None):
+        import cublade_b200 as cb
+
+        a, b = i % self.sets, (i + 1) % self.sets
+        if events:
+            events[0].record()
+        self.qt[a] = self._q(self.x[a])
+        if events:
+            events[1].record()
+        y = cb.dequantize_tensor(self.qt[b])
+        if events:
+            events[2].record()
+        return y
+
+    def step_e2e(self, i):
+        import cublade_b200 as cb
+
+        x = self.x_host.to(self.device, non_blocking=True)
+        y = cb.dequantize_tensor(self._q(x))
+        self.y_host.copy_(y, non_blocking=True)
+        return y
+
+    def cpu_step(self, x_cpu):
+        from oracle import oracle as O
+
+        q, s = O.fp8_quantize(x_cpu)
+        return O.fp8_dequantize(q, s, torch.bfloat16)
+
+
+class Int8GroupWorkload(Int8ChannelWorkload):
+    """INT8 per-group (128 along the last axis) quantize + dequantize of bf16 Student-t activations."""
+
+    name = "int8_group"
+    dominant = "quant_segments_kernel (one-pass per-group INT8 quantize)"
+
+    def __init__(self, device, rows=16384, cols=8192, sets=2, group=128):
+        from cublade_b200 import workloads as W
+
+        self.rows, self.cols, self.sets, self.group = rows, cols, sets, group
+        x_host = W.int8_group_case(rows, cols)
+        self._host_buffers(x_host, device, sets)
+        self.n = rows * cols
+        self.q_bytes = self.n * 3 + (self.n // group) * 4
+        self.dq_bytes = self.q_bytes
+        self.bytes_per_step = self.q_bytes + self.dq_bytes
+        self.device = device
+        self.qt = [None] * sets
+        self.launches_per_step = 2
+        self.kernel_ms = []
+
+    def config(self):
+        c = super().config()
+        c["workload"] = f"int8_per_group_{self.group}_quant+dequant bf16 {self.rows}x{self.cols} (Student-t nu=3 x0.5)"
+        c["seed"] = 2
+        return c
+
+    def _q(self, x):
+        import cublade_b200 as cb
+
+        return cb.quantize_tensor(x, dtype=torch.int8, mode="group", group_size=self.group, ch_axis=-1)
+
+    prime = Fp8TensorWorkload.prime
+    step = Fp8TensorWorkload.step
+    step_e2e = Fp8TensorWorkload.step_e2e
+
+    def cpu_step(self, x_cpu):
+        from oracle import oracle as O
+
+        q, s = O.int8_quantize_group(x_cpu.view(-1, self.group), self.group)
+        return O.int8_dequantize_rows(q, s, torch.bfloat16)
+
+
+WORKLOADS = {"int8_channel": Int8ChannelWorkload, "fp8_tensor": Fp8TensorWorkload, "int8_group": Int8GroupWorkload}
+
+
+# --------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """CPU formulation of the same step on this host's cores (rank 0 only; other ranks do nothing)."""
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload](None)
+    x = wl.cpu_input()
+    cores = torch.get_num_threads()
+    for _ in range(max(1, min(args.warmup, 2))):
+        wl.cpu_step(x)
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        wl.cpu_step(x)
+    dt = (time.perf_counter() - t0) / steps
+    value = wl.bytes_per_step / dt / 1e9
+    sample = f"full tensor {tuple(x.shape)}, mean of {steps} steps (steps capped at 20), PyTorch CPU formulation"
+    cfg = wl.config()
+    cfg["l2_policy"] = "n/a (CPU)"
+    print(json.dumps({
+        "impl": "reference", "metric": "quant/dequant GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def cpu_baseline(wl, budget_s=12.0):
+    cores = torch.get_num_threads()
+    x = wl.cpu_input()
+    wl.cpu_step(x)  # warm-up
+    best, reps, t_all = None, 0, time.perf_counter()
+    while reps < 3 or (time.perf_counter() - t_all < budget_s and reps < 10):
+        t0 = time.perf_counter()
+        wl.cpu_step(x)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+        reps += 1
+    return {"value": wl.bytes_per_step / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"full {wl.rows}x{wl.cols} tensor, best of {reps} (PyTorch CPU formulation of the reference ops)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="cublade_b200", choices=["cublade_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    from cublade_b200 import _native as N
+
+    N.lib()  # fail loudly if the extension is missing
+    warmup = max(args.warmup, 3)
+    wl = WORKLOADS[args.workload](device)
+    wl.prime()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -----------------------------------------------------------
+    for i in range(warmup):
+        wl.step(i)
+    K = args.steps
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    barrier()
+    launches0 = N.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for i in range(K):
+            wl.step(i, evs[i])
+        barrier()
+    launches = N.launch_count() - launches0
+    total_ms = evs[0][0].elapsed_time(evs[-1][2])
+    q_ms = [e[0].elapsed_time(e[1]) for e in evs]
+    dq_ms = [e[1].elapsed_time(e[2]) for e in evs]
+    ms_per_step = total_ms / K
+    if dist is not None:
+        t = torch.tensor([ms_per_step], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_per_step = float(t.item())
+    value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API from pinned host memory -----------------------------
+    e2e_steps = max(3, min(K, 20))
+    for i in range(3):
+        wl.step_e2e(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        wl.step_e2e(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * wl.bytes_per_step / (e2e_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        peaks = _peaks()
+        q_avg = sum(q_ms) / len(q_ms)
+        dq_avg = sum(dq_ms) / len(dq_ms)
+        achieved = wl.q_bytes / (q_avg * 1e-3) / 1e9
+        out = {
+            "metric": "quant/dequant GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": K,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": wl.e2e_h2d, "d2h_bytes_per_step": wl.e2e_d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": wl.dominant, "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                         "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "algorithmic_bytes_per_launch": wl.q_bytes,
+                         "avg_launch_us": q_avg * 1e3, "frac_of_nominal_8000": achieved / 8000.0},
+            "kernels": {"quantize": {"avg_us": q_avg * 1e3, "gbs": achieved},
+                        "dequantize": {"avg_us": dq_avg * 1e3, "gbs": wl.dq_bytes / (dq_avg * 1e-3) / 1e9,
+                                       "frac": wl.dq_bytes / (dq_avg * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
+        }
+        if not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(wl)
+        print(json.dumps(out))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,60 @@
+"""Bindings for symmetric INT8 quantization: per tensor, per channel (axis 0), per group
+(same names and contracts as cublade/bindings/cuda/quantize_int8.py:18-87).
+
+Arithmetic for every reduction domain D (tensor / row / group):
+``inv = fp32(127 / max(amax_D, eps))``, ``q = clamp(round_half_even(float(x) * inv), -127, 127)``,
+``scale_D = fp32(1 / inv)`` (quantize_int8.cu:120-126).
+"""
+from __future__ import annotations
+
+import torch
+
+from ... import _native as N
+from ._common import check_quant_input, require
+
+_ALLOWED = (torch.float16, torch.bfloat16, torch.float32)
+_TEXT = "torch.float16, torch.bfloat16, or torch.float32"
+
+
+def quantize_per_tensor_int8(x: torch.Tensor, eps: float = 1e-12) -> tuple[torch.Tensor, torch.Tensor]:
+    """One scale for the whole tensor. Returns ``(q int8 like x, scale 0-d float32)``."""
+    check_quant_input(x, _ALLOWED, _TEXT)
+    with torch.cuda.device(x.device):
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        scale = torch.empty((), dtype=torch.float32, device=x.device)
+        amax = torch.empty((), dtype=torch.float32, device=x.device)
+        N.check(N.lib().cb_quantize_per_tensor_int8(x.data_ptr(), N.dtype_code(x.dtype), x.numel(), float(eps),
+                                                    q.data_ptr(), scale.data_ptr(), amax.data_ptr(), N.stream_ptr(x)))
+    return q, scale
+
+
+def quantize_per_channel_int8(x: torch.Tensor, eps: float = 1e-12) -> tuple[torch.Tensor, torch.Tensor]:
+    """One scale per index of axis 0. ``x`` is viewed as ``[C, F]``; ``F * element_size`` must be
+    a multiple of 16 (RuntimeError otherwise, as in the reference). Returns ``(q, scale[C])``."""
+    check_quant_input(x, _ALLOWED, _TEXT)
+    require(x.dim() >= 1, "x must have at least 1 dim for per-channel quant")
+    C = x.size(0)
+    F = x.numel() // C if C > 0 else 0
+    with torch.cuda.device(x.device):
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        scale = torch.empty((C,), dtype=torch.float32, device=x.device)
+        N.check(N.lib().cb_quantize_per_channel_int8(x.data_ptr(), N.dtype_code(x.dtype), C, F, float(eps),
+                                                     q.data_ptr(), scale.data_ptr(), N.stream_ptr(x)))
+    return q, scale
+
+
+def quantize_per_group_int8(x_grouped: torch.Tensor, group_size: int, eps: float = 1e-12) -> tuple[torch.Tensor, torch.Tensor]:
+    """One scale per row of the contiguous ``[num_groups, group_size]`` input.
+    ``group_size`` must equal ``x_grouped.size(1)`` and lie in (0, 4096]."""
+    check_quant_input(x_grouped, _ALLOWED, _TEXT)
+    require(x_grouped.dim() == 2, "x_grouped must be 2D (num_groups, group_size)")
+    require(x_grouped.size(1) == group_size, "x_grouped.size(1) must equal group_size")
+    require(0 < group_size <= 4096, "group_size must be in (0, 4096]")
+    G = x_grouped.size(0)
+    with torch.cuda.device(x_grouped.device):
+        q = torch.empty(x_grouped.shape, dtype=torch.int8, device=x_grouped.device)
+        scale = torch.empty((G,), dtype=torch.float32, device=x_grouped.device)
+        N.check(N.lib().cb_quantize_per_group_int8(x_grouped.data_ptr(), N.dtype_code(x_grouped.dtype), G,
+                                                   int(group_size), float(eps), q.data_ptr(), scale.data_ptr(),
+                                                   N.stream_ptr(x_grouped)))
+    return q, scale

@@ -1,0 +1,196 @@
+// extern "C" surface of libcublade_b200.so: argument validation, error text,
+// launch accounting.  The declarations and the reference interface each entry
+// point replaces live in include/cublade_b200.h.
+
+#include "../../include/cublade_b200.h"
+#include "launch.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+
+int32_t fail(cb_status st, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return (int32_t)st;
+}
+
+int32_t cuda_result(cudaError_t e, const char* what, int launches) {
+    if (e != cudaSuccess) return fail(CB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    g_launches.fetch_add(launches, std::memory_order_relaxed);
+    return CB_OK;
+}
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool is_half_like(int32_t dt) { return dt == CB_F16 || dt == CB_BF16; }
+inline bool is_float_like(int32_t dt) { return dt == CB_F16 || dt == CB_BF16 || dt == CB_F32; }
+
+int32_t quantize_per_tensor(const char* name, const void* x, int32_t dtype, int64_t n, float eps, int code, void* q,
+                            float* scale, float* amax, void* stream) {
+    if (!scale || !amax || n < 0 || (n > 0 && (!x || !q))) return fail(CB_ERR_ARGUMENT, "%s: null pointer or n < 0", name);
+    cudaStream_t s = as_stream(stream);
+    cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+    if (e != cudaSuccess) return cuda_result(e, name, 0);
+    e = cb::launch_amax_tensor(x, dtype, n, amax, s);
+    if (e != cudaSuccess) return cuda_result(e, name, 0);
+    e = cb::launch_cast_tensor(x, dtype, n, amax, eps, code, q, scale, s);
+    return cuda_result(e, name, n > 0 ? 2 : 1);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t cb_version(void) { return 100; }
+const char* cb_last_error(void) { return g_err; }
+int64_t cb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int32_t cb_quantize_per_tensor_fp8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
+                                   float* amax_scratch, void* stream) {
+    if (!is_half_like(dtype)) return fail(CB_ERR_DTYPE, "cb_quantize_per_tensor_fp8: x must be float16 or bfloat16");
+    return quantize_per_tensor("cb_quantize_per_tensor_fp8", x, dtype, n, eps, cb::kCodeE4M3, q, scale, amax_scratch,
+                               stream);
+}
+
+int32_t cb_quantize_per_tensor_int8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
+                                    float* amax_scratch, void* stream) {
+    if (!is_float_like(dtype))
+        return fail(CB_ERR_DTYPE, "cb_quantize_per_tensor_int8: x must be float16, bfloat16 or float32");
+    return quantize_per_tensor("cb_quantize_per_tensor_int8", x, dtype, n, eps, cb::kCodeInt8, q, scale, amax_scratch,
+                               stream);
+}
+
+int32_t cb_amax_abs(const void* x, int32_t dtype, int64_t n, float* amax, void* stream) {
+    if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "cb_amax_abs: bad dtype");
+    if (!amax || n < 0 || (n > 0 && !x)) return fail(CB_ERR_ARGUMENT, "cb_amax_abs: null pointer or n < 0");
+    return cuda_result(cb::launch_amax_tensor(x, dtype, n, amax, as_stream(stream)), "cb_amax_abs", n > 0 ? 1 : 0);
+}
+
+int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float* amax, float eps, int32_t code_kind,
+                           void* q, float* scale, void* stream) {
+    if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "cb_cast_per_tensor: bad dtype");
+    if (code_kind != cb::kCodeInt8 && code_kind != cb::kCodeE4M3)
+        return fail(CB_ERR_ARGUMENT, "cb_cast_per_tensor: code_kind must be 0 (int8) or 1 (e4m3)");
+    if (code_kind == cb::kCodeE4M3 && !is_half_like(dtype))
+        return fail(CB_ERR_DTYPE, "cb_cast_per_tensor: e4m3 needs float16 or bfloat16 input");
+    if (!amax || !scale || n < 0 || (n > 0 && (!x || !q)))
+        return fail(CB_ERR_ARGUMENT, "cb_cast_per_tensor: null pointer or n < 0");
+    return cuda_result(cb::launch_cast_tensor(x, dtype, n, amax, eps, code_kind, q, scale, as_stream(stream)),
+                       "cb_cast_per_tensor", 1);
+}
+
+int32_t cb_quantize_per_channel_int8(const void* x, int32_t dtype, int64_t C, int64_t F, float eps, void* q,
+                                     float* scale, void* stream) {
+    if (!is_float_like(dtype))
+        return fail(CB_ERR_DTYPE, "cb_quantize_per_channel_int8: x must be float16, bfloat16 or float32");
+    if (C < 0 || F < 0) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_channel_int8: negative size");
+    if ((F * cb::dtype_size(dtype)) % 16 != 0)
+        return fail(CB_ERR_ALIGNMENT,
+                    "per-channel quant requires inner stride F * element_size to be a multiple of 16; got F=%lld "
+                    "element_size=%d",
+                    (long long)F, cb::dtype_size(dtype));
+    if (C == 0 || F == 0) return CB_OK;
+    if (!x || !q || !scale) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_channel_int8: null pointer");
+    return cuda_result(cb::launch_quant_segments(x, dtype, C, F, eps, cb::kCodeInt8, q, scale, as_stream(stream)),
+                       "cb_quantize_per_channel_int8", 1);
+}
+
+int32_t cb_quantize_per_group_int8(const void* x, int32_t dtype, int64_t num_groups, int64_t group_size, float eps,
+                                   void* q, float* scale, void* stream) {
+    if (!is_float_like(dtype))
+        return fail(CB_ERR_DTYPE, "cb_quantize_per_group_int8: x must be float16, bfloat16 or float32");
+    if (group_size <= 0 || group_size > 4096) return fail(CB_ERR_RANGE, "group_size must be in (0, 4096]");
+    if (num_groups < 0) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_group_int8: negative size");
+    if (num_groups == 0) return CB_OK;
+    if (!x || !q || !scale) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_group_int8: null pointer");
+    return cuda_result(
+        cb::launch_quant_segments(x, dtype, num_groups, group_size, eps, cb::kCodeInt8, q, scale, as_stream(stream)),
+        "cb_quantize_per_group_int8", 1);
+}
+
+static int32_t dequant_common(const char* name, const void* q, int code, const float* scale, int64_t n,
+                              int64_t seg_len, int32_t out_dtype, void* y, void* stream) {
+    if (!is_half_like(out_dtype)) return fail(CB_ERR_DTYPE, "%s: out_dtype must be float16 or bfloat16", name);
+    if (n < 0) return fail(CB_ERR_ARGUMENT, "%s: negative size", name);
+    if (n == 0) return CB_OK;
+    if (!q || !scale || !y) return fail(CB_ERR_ARGUMENT, "%s: null pointer", name);
+    return cuda_result(cb::launch_dequant(q, code, scale, n, seg_len, out_dtype, y, as_stream(stream)), name, 1);
+}
+
+int32_t cb_dequantize_per_tensor_fp8(const void* q, const float* scale, int64_t n, int32_t out_dtype, void* y,
+                                     void* stream) {
+    return dequant_common("cb_dequantize_per_tensor_fp8", q, cb::kCodeE4M3, scale, n, 0, out_dtype, y, stream);
+}
+
+int32_t cb_dequantize_per_tensor_int8(const void* q, const float* scale, int64_t n, int32_t out_dtype, void* y,
+                                      void* stream) {
+    return dequant_common("cb_dequantize_per_tensor_int8", q, cb::kCodeInt8, scale, n, 0, out_dtype, y, stream);
+}
+
+int32_t cb_dequantize_per_channel_int8(const void* q, const float* scale, int64_t C, int64_t F, int32_t out_dtype,
+                                       void* y, void* stream) {
+    if (C < 0 || F < 0) return fail(CB_ERR_ARGUMENT, "cb_dequantize_per_channel_int8: negative size");
+    if (F % 8 != 0)
+        return fail(CB_ERR_ALIGNMENT,
+                    "per-channel dequant requires inner stride F to be a multiple of 8; got F=%lld", (long long)F);
+    return dequant_common("cb_dequantize_per_channel_int8", q, cb::kCodeInt8, scale, C * F, F, out_dtype, y, stream);
+}
+
+int32_t cb_dequantize_per_group_int8(const void* q, const float* scale, int64_t num_groups, int64_t group_size,
+                                     int32_t out_dtype, void* y, void* stream) {
+    if (group_size <= 0 || group_size > 4096) return fail(CB_ERR_RANGE, "group_size must be in (0, 4096]");
+    if (num_groups < 0) return fail(CB_ERR_ARGUMENT, "cb_dequantize_per_group_int8: negative size");
+    return dequant_common("cb_dequantize_per_group_int8", q, cb::kCodeInt8, scale, num_groups * group_size,
+                          group_size, out_dtype, y, stream);
+}
+
+size_t cb_w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K) { return cb::w8a16_workspace_bytes(M, N, K); }
+
+int32_t cb_w8a16_linear(const void* x, int64_t M, int64_t K, int64_t ldx, const void* wq, int64_t N,
+                        const void* scales, int32_t scales_dtype, const void* bias, int32_t bias_dtype,
+                        const void* xo, int64_t ldxo, const void* wo, int64_t KO, void* y, int64_t ldy,
+                        int32_t act_dtype, void* workspace, size_t workspace_bytes, int32_t path, void* stream) {
+    if (!is_half_like(act_dtype)) return fail(CB_ERR_DTYPE, "cb_w8a16_linear: activations must be float16 or bfloat16");
+    if (!is_float_like(scales_dtype)) return fail(CB_ERR_DTYPE, "cb_w8a16_linear: bad scales dtype");
+    if (bias && !is_float_like(bias_dtype)) return fail(CB_ERR_DTYPE, "cb_w8a16_linear: bad bias dtype");
+    if (M < 0 || N < 0 || K < 0 || KO < 0) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: negative size");
+    if (M == 0 || N == 0) return CB_OK;
+    if (!x || !wq || !scales || !y) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: null pointer");
+    if (KO > 0 && (!xo || !wo)) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: KO > 0 needs xo and wo");
+    if (ldx < K || ldy < N || (KO > 0 && ldxo < KO)) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: row stride too small");
+    if (path < 0 || path > 2) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: path must be 0, 1 or 2");
+    const size_t need = cb::w8a16_workspace_bytes(M, N, K);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(CB_ERR_WORKSPACE, "cb_w8a16_linear: workspace of %zu bytes required", need);
+    cb::W8A16Args a;
+    a.x = x; a.M = M; a.K = K; a.ldx = ldx;
+    a.wq = static_cast<const int8_t*>(wq); a.N = N;
+    a.scales = scales; a.scales_dtype = scales_dtype;
+    a.bias = bias; a.bias_dtype = bias_dtype;
+    a.xo = KO > 0 ? xo : nullptr; a.wo = KO > 0 ? wo : nullptr; a.KO = KO; a.ldxo = ldxo;
+    a.y = y; a.ldy = ldy; a.act_dtype = act_dtype;
+    a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+    cudaError_t e = cb::launch_w8a16(a, path, as_stream(stream));
+    if (e == cudaErrorNotSupported)
+        return fail(CB_ERR_UNSUPPORTED, "cb_w8a16_linear: shape/alignment not supported by the requested path");
+    return cuda_result(e, "cb_w8a16_linear", 1);
+}
+
+int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols, void* dst,
+                          int64_t ld_dst, int32_t elem_size, void* stream) {
+    if (M < 0 || ncols < 0) return fail(CB_ERR_ARGUMENT, "cb_gather_columns: negative size");
+    if (elem_size != 2 && elem_size != 4) return fail(CB_ERR_ARGUMENT, "cb_gather_columns: elem_size must be 2 or 4");
+    if (M == 0 || ncols == 0) return CB_OK;
+    if (!src || !cols || !dst) return fail(CB_ERR_ARGUMENT, "cb_gather_columns: null pointer");
+    return cuda_result(cb::launch_gather_cols(src, M, ld_src, cols, ncols, dst, ld_dst, elem_size, as_stream(stream)),
+                       "cb_gather_columns", 1);
+}
+
+}  // extern "C"

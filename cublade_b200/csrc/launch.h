@@ -1,0 +1,63 @@
+// Internal launch interface between the C-ABI layer (cabi.cu) and the kernel
+// translation units.  Everything here takes raw device pointers and a stream;
+// nothing allocates.  Return value: cudaError_t of the launch (cudaSuccess = 0).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+
+namespace cb {
+
+enum DType : int { kF16 = 0, kBF16 = 1, kF32 = 2 };
+enum CodeKind : int { kCodeInt8 = 0, kCodeE4M3 = 1 };
+
+inline int dtype_size(int dt) { return dt == kF32 ? 4 : 2; }
+
+// number of SMs of the current device (cached per device)
+int sm_count();
+
+// ---- per-tensor (two phase) ------------------------------------------------
+// amax[0] = max(amax[0], max|x|); amax must hold a non-negative float (0 to start).
+cudaError_t launch_amax_tensor(const void* x, int dtype, int64_t n, float* amax, cudaStream_t s);
+// codes = encode(x * qmax/max(amax,eps)); scale_out[0] = 1/(qmax/max(amax,eps)).
+cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float* amax, float eps, int code,
+                               void* q, float* scale_out, cudaStream_t s);
+
+// ---- per-segment (rows of a [nseg, L] matrix: channels or groups), one pass --
+cudaError_t launch_quant_segments(const void* x, int dtype, int64_t nseg, int64_t L, float eps, int code, void* q,
+                                  float* scale_out, cudaStream_t s);
+
+// ---- dequantize -------------------------------------------------------------
+// seg_len == 0: one scale for the whole tensor; otherwise scale[i / seg_len].
+cudaError_t launch_dequant(const void* q, int code, const float* scale, int64_t n, int64_t seg_len, int out_dtype,
+                           void* y, cudaStream_t s);
+
+// ---- W8A16 linear -------------------------------------------------------------
+struct W8A16Args {
+    const void* x;        // [M, K] bf16/f16 activations, row stride ldx elements
+    int64_t M, K, ldx;
+    const int8_t* wq;     // [N, K] int8 codes, row-major
+    int64_t N;
+    const void* scales;   // [N] per-output-channel scale
+    int scales_dtype;     // kF16 / kBF16 / kF32
+    const void* bias;     // [N] or nullptr
+    int bias_dtype;
+    // optional LLM.int8 side product: y += xo[M, KO] . wo[N, KO]^T (un-scaled)
+    const void* xo;       // [M, KO] same dtype as x, row stride ldxo
+    const void* wo;       // [N, KO] same dtype as x, row-major
+    int64_t KO, ldxo;
+    void* y;              // [M, N] same dtype as x, row stride ldy
+    int64_t ldy;
+    int act_dtype;        // kBF16 or kF16
+    void* workspace;      // may be nullptr when workspace_bytes == 0
+    size_t workspace_bytes;
+};
+size_t w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+// path: 0 = automatic, 1 = weight-streaming (skinny M) kernel, 2 = tcgen05 GEMM
+cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s);
+// gathers columns: dst[m, j] = src[m, cols[j]] (activation re-pack for the outlier split)
+cudaError_t launch_gather_cols(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
+                               void* dst, int64_t ld_dst, int elem_size, cudaStream_t s);
+
+}  // namespace cb

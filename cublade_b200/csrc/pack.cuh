@@ -1,0 +1,248 @@
+// Pack vocabulary shared by every quantize / dequantize kernel in this library.
+//
+// One *pack* is 16 bytes of input: 8 half / bf16 lanes or 4 fp32 lanes, moved
+// with a single 128-bit memory instruction.  `DTypeTraits<T>` holds the per
+// dtype conversions, `Pack16<T>` aliases the 16 bytes as raw bits or lanes,
+// and the free functions below turn a pack into quantized codes (or codes
+// back into a pack).  It plays the role of the reference's
+// cublade/kernels/cuda/quantization/fp8_pack.cuh:20-88 and int8_pack.cuh:23-100
+// (DTypeTraits / Pack16 / Pack16Int8 / PackInT / LanesPerInt4 /
+// round_half_even_clamp_int8), re-cut for kernels that keep several packs in
+// flight per thread.
+//
+// Arithmetic contract (the bit-exactness gate):
+//   * every product is a single fp32 multiply (no FMA contraction, no
+//     fast-math, no flush-to-zero) -- build without --use_fast_math;
+//   * reciprocal scales use IEEE round-to-nearest division (__fdiv_rn), which
+//     equals the reference's "divide in fp64, narrow to fp32" route because a
+//     quotient of two fp32 numbers needs at most 2*24+2 bits to be rounded
+//     once correctly;
+//   * INT8 codes: cvt.rni.s32.f32 then clamp to [-127, 127];
+//   * FP8 codes:  cvt.rn.satfinite.e4m3x2.f32 on the fp32 product.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace cb {
+
+constexpr float kInt8Qmax = 127.0f;
+constexpr float kE4M3Qmax = 448.0f;
+
+// ---------------------------------------------------------------------------
+// DTypeTraits<T>: lanes per 16-byte pack and scalar conversions.
+// ---------------------------------------------------------------------------
+template <typename T>
+struct DTypeTraits;
+
+template <>
+struct DTypeTraits<__half> {
+    static constexpr int kLanes = 8;
+    __device__ __forceinline__ static float to_float(__half v) { return __half2float(v); }
+    __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
+    // two lanes packed in one 32-bit word -> two fp32
+    __device__ __forceinline__ static float2 word_to_float2(uint32_t w) {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+    __device__ __forceinline__ static uint32_t float2_to_word(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+
+template <>
+struct DTypeTraits<__nv_bfloat16> {
+    static constexpr int kLanes = 8;
+    __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+    // bf16 is the top half of an fp32: widening is two integer ops, exact.
+    __device__ __forceinline__ static float2 word_to_float2(uint32_t w) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+    __device__ __forceinline__ static uint32_t float2_to_word(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+
+template <>
+struct DTypeTraits<float> {
+    static constexpr int kLanes = 4;
+    __device__ __forceinline__ static float to_float(float v) { return v; }
+    __device__ __forceinline__ static float from_float(float v) { return v; }
+};
+
+// ---------------------------------------------------------------------------
+// Pack16<T>: 16 bytes viewed as raw bits, 32-bit words, or lanes of T.
+// ---------------------------------------------------------------------------
+template <typename T>
+union Pack16 {
+    uint4 raw;
+    uint32_t w[4];
+    T lane[DTypeTraits<T>::kLanes];
+};
+
+// 16 quantized codes (int8 or e4m3) in one 128-bit word; 8 codes in 64 bits.
+union Codes16 {
+    uint4 raw;
+    uint2 half8[2];
+    uint8_t c[16];
+};
+
+// Unpack a pack into fp32 lanes (exact for every supported T).
+template <typename T>
+__device__ __forceinline__ void pack_to_floats(const uint4& raw, float (&f)[DTypeTraits<T>::kLanes]) {
+    if constexpr (DTypeTraits<T>::kLanes == 4) {
+        f[0] = __uint_as_float(raw.x);
+        f[1] = __uint_as_float(raw.y);
+        f[2] = __uint_as_float(raw.z);
+        f[3] = __uint_as_float(raw.w);
+    } else {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 p = DTypeTraits<T>::word_to_float2(w[k]);
+            f[2 * k] = p.x;
+            f[2 * k + 1] = p.y;
+        }
+    }
+}
+
+// max |lane| of a pack, NaN lanes dropped (fmaxf returns the non-NaN operand).
+template <typename T>
+__device__ __forceinline__ float pack_absmax(const uint4& raw, float running) {
+    constexpr int L = DTypeTraits<T>::kLanes;
+    float f[L];
+    pack_to_floats<T>(raw, f);
+#pragma unroll
+    for (int k = 0; k < L; ++k) running = fmaxf(running, fabsf(f[k]));
+    return running;
+}
+
+// Warp-shuffle max over WIDTH adjacent lanes (WIDTH a power of two <= 32).
+template <int WIDTH>
+__device__ __forceinline__ float team_max(float v) {
+#pragma unroll
+    for (int off = WIDTH / 2; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// Scalar code conversions.
+// ---------------------------------------------------------------------------
+// round-half-even then clamp to the symmetric range; NaN -> 0 (cvt.rni of NaN).
+__device__ __forceinline__ int round_half_even_clamp_int8(float v) {
+    int r = __float2int_rn(v);
+    r = max(r, -127);
+    r = min(r, 127);
+    return r;
+}
+
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
+    return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t c) {
+    __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)c, __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&hr));
+}
+
+// ---------------------------------------------------------------------------
+// Whole-pack conversions.  Code kinds.
+// ---------------------------------------------------------------------------
+struct Int8Code {
+    static constexpr float kQmax = kInt8Qmax;
+    __device__ __forceinline__ static uint32_t encode4(float a, float b, float c, float d) {
+        const uint32_t x = (uint32_t)round_half_even_clamp_int8(a) & 0xffu;
+        const uint32_t y = (uint32_t)round_half_even_clamp_int8(b) & 0xffu;
+        const uint32_t z = (uint32_t)round_half_even_clamp_int8(c) & 0xffu;
+        const uint32_t w = (uint32_t)round_half_even_clamp_int8(d);
+        return x | (y << 8) | (z << 16) | (w << 24);
+    }
+    __device__ __forceinline__ static uint8_t encode1(float a) { return (uint8_t)round_half_even_clamp_int8(a); }
+    // four codes in one word -> four fp32
+    __device__ __forceinline__ static void decode4(uint32_t w, float (&f)[4]) {
+        f[0] = (float)(int)(int8_t)(w & 0xffu);
+        f[1] = (float)(int)(int8_t)((w >> 8) & 0xffu);
+        f[2] = (float)(int)(int8_t)((w >> 16) & 0xffu);
+        f[3] = (float)((int)w >> 24);
+    }
+    __device__ __forceinline__ static float decode1(uint8_t c) { return (float)(int)(int8_t)c; }
+};
+
+struct E4M3Code {
+    static constexpr float kQmax = kE4M3Qmax;
+    __device__ __forceinline__ static uint32_t encode4(float a, float b, float c, float d) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+        return lo | (hi << 16);
+    }
+    __device__ __forceinline__ static uint8_t encode1(float a) { return float_to_e4m3(a); }
+    __device__ __forceinline__ static void decode4(uint32_t w, float (&f)[4]) {
+        __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xffffu), __NV_E4M3);
+        __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
+        float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+        float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    }
+    __device__ __forceinline__ static float decode1(uint8_t c) { return e4m3_to_float(c); }
+};
+
+// Quantize one pack: lanes * inv -> codes.  16-bit inputs give 8 codes (uint2),
+// fp32 inputs give 4 codes (one word, returned in .x).
+template <typename T, typename Code>
+__device__ __forceinline__ uint2 pack_encode(const uint4& raw, float inv) {
+    constexpr int L = DTypeTraits<T>::kLanes;
+    float f[L];
+    pack_to_floats<T>(raw, f);
+#pragma unroll
+    for (int k = 0; k < L; ++k) f[k] = __fmul_rn(f[k], inv);
+    uint2 out;
+    out.x = Code::encode4(f[0], f[1], f[2], f[3]);
+    if constexpr (L == 8) out.y = Code::encode4(f[4], f[5], f[6], f[7]);
+    else out.y = 0u;
+    return out;
+}
+
+// Dequantize 8 codes (uint2) into one 16-byte pack of OutT (half / bf16).
+template <typename OutT, typename Code>
+__device__ __forceinline__ uint4 codes_decode8(const uint2& codes, float s) {
+    float a[4], b[4];
+    Code::decode4(codes.x, a);
+    Code::decode4(codes.y, b);
+    uint4 out;
+    out.x = DTypeTraits<OutT>::float2_to_word(__fmul_rn(a[0], s), __fmul_rn(a[1], s));
+    out.y = DTypeTraits<OutT>::float2_to_word(__fmul_rn(a[2], s), __fmul_rn(a[3], s));
+    out.z = DTypeTraits<OutT>::float2_to_word(__fmul_rn(b[0], s), __fmul_rn(b[1], s));
+    out.w = DTypeTraits<OutT>::float2_to_word(__fmul_rn(b[2], s), __fmul_rn(b[3], s));
+    return out;
+}
+
+// The two numbers every quantizer derives from an amax:
+//   inv   = qmax / max(amax, eps)   (what the codes are multiplied by)
+//   scale = 1 / inv                 (what dequantize multiplies by; NOT amax/qmax)
+// Reference: quantize_per_tensor_fp8.cu:99-102, quantize_int8.cu:120-126.
+struct InvScale {
+    float inv;
+    float scale;
+};
+template <typename Code>
+__device__ __forceinline__ InvScale inv_and_scale(float amax, float eps) {
+    InvScale r;
+    r.inv = __fdiv_rn(Code::kQmax, fmaxf(amax, eps));
+    r.scale = __fdiv_rn(1.0f, r.inv);
+    return r;
+}
+
+// Streaming 128-bit / 64-bit / 32-bit global accesses.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint4 ld_keep16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint2 ld_stream8(const void* p) { return __ldcs(reinterpret_cast<const uint2*>(p)); }
+__device__ __forceinline__ void st_stream16(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+__device__ __forceinline__ void st_stream8(void* p, uint2 v) { __stcs(reinterpret_cast<uint2*>(p), v); }
+__device__ __forceinline__ void st_stream4(void* p, uint32_t v) { __stcs(reinterpret_cast<uint32_t*>(p), v); }
+
+}  // namespace cb

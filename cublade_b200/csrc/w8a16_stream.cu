@@ -1,0 +1,361 @@
+// W8A16 linear, weight-streaming kernel for skinny activations (decode shapes).
+//
+//   y[m, n] = (sum_k x[m, k] * wq[n, k]) * scale[n] + sum_j xo[m, j] * wo[n, j] + bias[n]
+//
+// For M <= 64 the op is bound by streaming the N*K int8 weights from HBM once,
+// so the kernel is built around that stream: each warp owns 16 weight rows and
+// a slice of K, pulls its int8 rows straight from global memory into registers
+// with 128-bit loads (no shared-memory staging, no transpose, no bf16 copy of
+// the weights -- the reference materialises both, cublade/quantization/linear.py:123-126
+// and cublade/bindings/triton/matmul.py:20-21), widens them to 16-bit floats in
+// registers and feeds warp-level mma.m16n8k16 with the weights as the 16-row
+// operand and up to 64 activation rows as the 8-column operand(s).
+//
+// The k index inside one 16-wide mma step is a free permutation as long as
+// both operands use the same one, so a thread's 16 contiguous weight bytes
+// (k = 16t .. 16t+15 of a 64-wide block, t = lane % 4) serve four mma steps
+// and the matching activations are its own 32 contiguous bytes of x.
+//
+// Four warps of a CTA split K four ways for one 16-row tile and reduce through
+// shared memory; the epilogue applies the per-row scale, adds the 16-bit side
+// product over the outlier columns and the bias, rounds once, and stores.
+
+#include "launch.h"
+#include "pack.cuh"
+
+namespace cb {
+
+namespace {
+
+constexpr int kWarps = 4;
+
+template <typename A>
+struct Act;
+template <>
+struct Act<__nv_bfloat16> {
+    // four int8 codes (one word) -> two words of bf16 pairs (c0,c1) (c2,c3)
+    __device__ __forceinline__ static void widen4(uint32_t c, uint32_t& lo, uint32_t& hi) {
+        // fp32 magic: 0x4B000000 | (code ^ 0x80) = 2^23 + code + 128; subtract 2^23 + 128; the
+        // result is a small integer, so its top 16 bits are its exact bf16 form.
+        const uint32_t u = c ^ 0x80808080u;
+        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+        lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+        hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+    }
+    __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct Act<__half> {
+    __device__ __forceinline__ static void widen4(uint32_t c, uint32_t& lo, uint32_t& hi) {
+        // fp16 magic: 0x6400 | (code ^ 0x80) = 1024 + code + 128; subtract 1152 (exact in fp16).
+        const uint32_t u = c ^ 0x80808080u;
+        const uint32_t p0 = __byte_perm(u, 0x64006400u, 0x7150);  // bytes: u0, 0x64, u1, 0x64
+        const uint32_t p1 = __byte_perm(u, 0x64006400u, 0x7352);
+        const __half2 k = __half2half2(__ushort_as_half((unsigned short)0x6480));  // 1152.0
+        __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&p0), k);
+        __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&p1), k);
+        lo = *reinterpret_cast<uint32_t*>(&a);
+        hi = *reinterpret_cast<uint32_t*>(&b);
+    }
+    __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    __device__ __forceinline__ static float to_float(__half v) { return __half2float(v); }
+    __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
+};
+
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+    if (dtype == kF32) return static_cast<const float*>(p)[i];
+    if (dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+struct StreamParams {
+    const void* x;
+    int64_t M, K, ldx;
+    const int8_t* wq;
+    int64_t N;
+    const void* scales;
+    int scales_dtype;
+    const void* bias;
+    int bias_dtype;
+    const void* xo;
+    const void* wo;
+    int64_t KO, ldxo;
+    void* y;
+    int64_t ldy;
+    int64_t m0;  // first activation row of this pass
+};
+
+// One 16-byte (VEC==16) / 8 / 4 / 1-byte-granular load of weight codes for row `r`, k in [k, k+VEC').
+// Returns the bytes as words; out-of-range parts are zero.
+template <int VEC>
+__device__ __forceinline__ void load_codes(const int8_t* __restrict__ row, int64_t k, int64_t K, bool row_ok,
+                                           uint32_t (&w)[VEC >= 4 ? VEC / 4 : 1]) {
+    constexpr int NW = VEC >= 4 ? VEC / 4 : 1;
+#pragma unroll
+    for (int i = 0; i < NW; ++i) w[i] = 0u;
+    if (!row_ok) return;
+    if constexpr (VEC == 16) {
+        if (k + 16 <= K) {
+            const uint4 v = __ldcs(reinterpret_cast<const uint4*>(row + k));
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+        }
+    } else if constexpr (VEC == 8) {
+        if (k + 8 <= K) {
+            const uint2 v = __ldcs(reinterpret_cast<const uint2*>(row + k));
+            w[0] = v.x; w[1] = v.y;
+        }
+    } else if constexpr (VEC == 4) {
+        if (k + 4 <= K) w[0] = __ldcs(reinterpret_cast<const uint32_t*>(row + k));
+    } else {
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (k + b < K) w[0] |= (uint32_t)(uint8_t)row[k + b] << (8 * b);
+    }
+}
+
+// Activations for the same k range: VEC' elements of 2 bytes -> words of pairs.
+template <typename A, int VEC>
+__device__ __forceinline__ void load_acts(const A* __restrict__ row, int64_t k, int64_t K, bool row_ok,
+                                          uint32_t (&w)[VEC >= 4 ? VEC / 2 : 2]) {
+    constexpr int NW = VEC >= 4 ? VEC / 2 : 2;
+#pragma unroll
+    for (int i = 0; i < NW; ++i) w[i] = 0u;
+    if (!row_ok) return;
+    if constexpr (VEC == 16) {
+        if (k + 16 <= K) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(row + k));
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(row + k + 8));
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+            w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
+    } else if constexpr (VEC == 8) {
+        if (k + 8 <= K) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(row + k));
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+        }
+    } else if constexpr (VEC == 4) {
+        if (k + 4 <= K) {
+            const uint2 a = __ldg(reinterpret_cast<const uint2*>(row + k));
+            w[0] = a.x; w[1] = a.y;
+        }
+    } else {
+        const unsigned short* r16 = reinterpret_cast<const unsigned short*>(row);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (k + b < K) w[b / 2] |= (uint32_t)r16[k + b] << (16 * (b & 1));
+    }
+}
+
+// VEC: bytes of weight codes a thread loads at once (16, 8, 4) or 1 for the
+// byte-wise path that accepts any K / alignment.  MT: activation 8-row tiles.
+template <typename A, int VEC, int MT>
+__global__ void __launch_bounds__(kWarps * 32) w8a16_stream_kernel(const StreamParams p) {
+    constexpr int KSTEP = VEC >= 4 ? VEC * 4 : 16;   // k covered by a warp per load round
+    constexpr int NSTEP = VEC >= 4 ? VEC / 4 : 1;    // mma k16-steps per load round
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n0 = (int64_t)blockIdx.x * 16;
+    const A* x = static_cast<const A*>(p.x);
+
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    const bool r0_ok = n0 + g < p.N, r1_ok = n0 + g + 8 < p.N;
+    const int8_t* w0 = p.wq + (n0 + g) * p.K;
+    const int8_t* w1 = p.wq + (n0 + g + 8) * p.K;
+    const int kper = VEC >= 4 ? VEC : 4;
+
+    // this warp's K slice: rounds of KSTEP, interleaved over the four warps in
+    // groups of 4 rounds so each warp streams contiguous 4*KSTEP-byte runs.
+    const int64_t nrounds = (p.K + KSTEP - 1) / KSTEP;
+    for (int64_t r = (int64_t)warp * 4; r < nrounds; r += kWarps * 4) {
+        uint32_t c0[4][VEC >= 4 ? VEC / 4 : 1], c1[4][VEC >= 4 ? VEC / 4 : 1];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t k = (r + u) * KSTEP + (int64_t)t * kper;
+            load_codes<VEC>(w0, k, p.K, r0_ok && (r + u) < nrounds, c0[u]);
+            load_codes<VEC>(w1, k, p.K, r1_ok && (r + u) < nrounds, c1[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t k = (r + u) * KSTEP + (int64_t)t * kper;
+            if ((r + u) >= nrounds) continue;
+            uint32_t xa[MT][VEC >= 4 ? VEC / 2 : 2];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int64_t m = p.m0 + mt * 8 + g;
+                load_acts<A, VEC>(x + m * p.ldx, k, p.K, m < p.M, xa[mt]);
+            }
+#pragma unroll
+            for (int s = 0; s < NSTEP; ++s) {
+                uint32_t a[4];
+                Act<A>::widen4(c0[u][s], a[0], a[2]);
+                Act<A>::widen4(c1[u][s], a[1], a[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) Act<A>::mma(acc[mt], a, xa[mt][2 * s], xa[mt][2 * s + 1]);
+            }
+        }
+    }
+
+    // per-row scale (rows g and g+8 of this tile)
+    const float s0 = r0_ok ? load_as_float(p.scales, p.scales_dtype, n0 + g) : 0.0f;
+    const float s1 = r1_ok ? load_as_float(p.scales, p.scales_dtype, n0 + g + 8) : 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        acc[mt][0] *= s0; acc[mt][1] *= s0;
+        acc[mt][2] *= s1; acc[mt][3] *= s1;
+    }
+
+    // 16-bit side product over the outlier columns, k16-steps dealt round-robin to the warps
+    if (p.KO > 0) {
+        const A* xo = static_cast<const A*>(p.xo);
+        const A* wo = static_cast<const A*>(p.wo);
+        const int64_t osteps = (p.KO + 15) / 16;
+        for (int64_t st = warp; st < osteps; st += kWarps) {
+            const int64_t k = st * 16 + t * 4;
+            uint32_t a0[2], a1[2];
+            load_acts<A, 1>(wo + (n0 + g) * p.KO, k, p.KO, r0_ok, a0);
+            load_acts<A, 1>(wo + (n0 + g + 8) * p.KO, k, p.KO, r1_ok, a1);
+            const uint32_t a[4] = {a0[0], a1[0], a0[1], a1[1]};
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int64_t m = p.m0 + mt * 8 + g;
+                uint32_t b[2];
+                load_acts<A, 1>(xo + m * p.ldxo, k, p.KO, m < p.M, b);
+                Act<A>::mma(acc[mt], a, b[0], b[1]);
+            }
+        }
+    }
+
+    // cross-warp reduction of the K split
+    __shared__ float red[kWarps - 1][MT * 4][32];
+    if (warp > 0) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red[warp - 1][mt * 4 + j][lane] = acc[mt][j];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int w = 0; w < kWarps - 1; ++w)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[mt][j] += red[w][mt * 4 + j][lane];
+
+    // D fragment: acc[mt][0..1] -> (row g, m = 2t, 2t+1), acc[mt][2..3] -> (row g+8, same m)
+    A* y = static_cast<A*>(p.y);
+    const float b0 = (p.bias && r0_ok) ? load_as_float(p.bias, p.bias_dtype, n0 + g) : 0.0f;
+    const float b1 = (p.bias && r1_ok) ? load_as_float(p.bias, p.bias_dtype, n0 + g + 8) : 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int64_t m = p.m0 + mt * 8 + 2 * t + j;
+            if (m >= p.M) continue;
+            if (r0_ok) y[m * p.ldy + n0 + g] = Act<A>::from_float(acc[mt][j] + b0);
+            if (r1_ok) y[m * p.ldy + n0 + g + 8] = Act<A>::from_float(acc[mt][2 + j] + b1);
+        }
+    }
+}
+
+template <typename Elem>
+__global__ void gather_cols_kernel(const Elem* __restrict__ src, int64_t M, int64_t ld_src,
+                                   const int64_t* __restrict__ cols, int64_t ncols, Elem* __restrict__ dst,
+                                   int64_t ld_dst) {
+    const int64_t total = M * ncols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / ncols, j = i - m * ncols;
+        dst[m * ld_dst + j] = src[m * ld_src + __ldg(cols + j)];
+    }
+}
+
+inline bool al(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+template <typename A, int VEC>
+cudaError_t stream_pick_mt(StreamParams p, cudaStream_t s) {
+    const unsigned grid = (unsigned)((p.N + 15) / 16);
+    int64_t m0 = 0;
+    while (m0 < p.M) {
+        const int64_t left = p.M - m0;
+        p.m0 = m0;
+        if (left > 32) {
+            w8a16_stream_kernel<A, VEC, 8><<<grid, kWarps * 32, 0, s>>>(p);
+            m0 += 64;
+        } else if (left > 16) {
+            w8a16_stream_kernel<A, VEC, 4><<<grid, kWarps * 32, 0, s>>>(p);
+            m0 += 32;
+        } else if (left > 8) {
+            w8a16_stream_kernel<A, VEC, 2><<<grid, kWarps * 32, 0, s>>>(p);
+            m0 += 16;
+        } else {
+            w8a16_stream_kernel<A, VEC, 1><<<grid, kWarps * 32, 0, s>>>(p);
+            m0 += 8;
+        }
+    }
+    return cudaPeekAtLastError();
+}
+
+template <typename A>
+cudaError_t stream_pick_vec(const StreamParams& p, cudaStream_t s) {
+    const bool base16 = al(p.wq, 16) && al(p.x, 16);
+    if (base16 && p.K % 16 == 0 && p.ldx % 8 == 0) return stream_pick_mt<A, 16>(p, s);
+    if (al(p.wq, 8) && al(p.x, 16) && p.K % 8 == 0 && p.ldx % 8 == 0) return stream_pick_mt<A, 8>(p, s);
+    if (al(p.wq, 4) && al(p.x, 8) && p.K % 4 == 0 && p.ldx % 4 == 0) return stream_pick_mt<A, 4>(p, s);
+    return stream_pick_mt<A, 1>(p, s);
+}
+
+}  // namespace
+
+cudaError_t launch_w8a16_stream(const W8A16Args& a, cudaStream_t s) {
+    StreamParams p;
+    p.x = a.x; p.M = a.M; p.K = a.K; p.ldx = a.ldx;
+    p.wq = a.wq; p.N = a.N;
+    p.scales = a.scales; p.scales_dtype = a.scales_dtype;
+    p.bias = a.bias; p.bias_dtype = a.bias_dtype;
+    p.xo = a.xo; p.wo = a.wo; p.KO = a.KO; p.ldxo = a.ldxo;
+    p.y = a.y; p.ldy = a.ldy; p.m0 = 0;
+    if (a.act_dtype == kBF16) return stream_pick_vec<__nv_bfloat16>(p, s);
+    if (a.act_dtype == kF16) return stream_pick_vec<__half>(p, s);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_gather_cols(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
+                               void* dst, int64_t ld_dst, int elem_size, cudaStream_t s) {
+    const int64_t total = M * ncols;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+    if (blocks < 1) blocks = 1;
+    if (elem_size == 2)
+        gather_cols_kernel<uint16_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), M, ld_src,
+                                                                        cols, ncols, static_cast<uint16_t*>(dst),
+                                                                        ld_dst);
+    else
+        gather_cols_kernel<uint32_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint32_t*>(src), M, ld_src,
+                                                                        cols, ncols, static_cast<uint32_t*>(dst),
+                                                                        ld_dst);
+    return cudaPeekAtLastError();
+}
+
+}  // namespace cb

@@ -1,0 +1,19 @@
+"""Drop-in for ``cublade.quantization`` (same public names as cublade/quantization/__init__.py:8-17)."""
+from .utils import *  # noqa: F401,F403
+from .tensor import QuantizedTensor
+from .dequantizers import dequantize_tensor
+from .linear import cuBladeW8A16LinearLayer, cubladeW8A16LinearLayer
+from .quantizers import quantize_tensor, quantize_model
+from .outlier_utils import detect_outlier_columns, separate_outliers, split_weights_by_outliers
+
+__all__ = [
+    "quantize_model",
+    "quantize_tensor",
+    "dequantize_tensor",
+    "QuantizedTensor",
+    "cuBladeW8A16LinearLayer",
+    "cubladeW8A16LinearLayer",
+    "detect_outlier_columns",
+    "separate_outliers",
+    "split_weights_by_outliers",
+]

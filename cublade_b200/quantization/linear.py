@@ -1,0 +1,112 @@
+"""``cuBladeW8A16LinearLayer``: int8 weights with one scale per output feature, 16-bit activations.
+
+Buffer names, dtypes and shapes (``int8_weights [out, in]``, ``scales [out]``, ``outlier_weights``,
+``normal_cols``, ``outlier_cols``) and the constructor / ``quantize`` / ``forward`` contract follow
+cublade/quantization/linear.py:8-137, so ``state_dict()`` is interchangeable.  The forward pass
+is one fused kernel (see ``bindings/w8a16.py``); it rounds once at the end, where the reference
+rounds after the GEMM, after the scale and after the bias.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..bindings.w8a16 import gather_columns, w8a16_linear
+from .outlier_utils import separate_outliers
+from .quantizers import quantize_tensor
+
+
+class cuBladeW8A16LinearLayer(nn.Module):
+    def __init__(self, in_features, out_features, bias=True, dtype=torch.bfloat16, handle_outliers=False,
+                 outlier_threshold=6.0):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.handle_outliers = handle_outliers
+        self.outlier_threshold = outlier_threshold
+
+        self.register_buffer("int8_weights", torch.empty(out_features, in_features, dtype=torch.int8))
+        self.register_buffer("scales", torch.ones(out_features, dtype=dtype))
+        # only populated by quantize() when handle_outliers=True
+        self.register_buffer("outlier_weights", None)
+        self.register_buffer("normal_cols", None)
+        self.register_buffer("outlier_cols", None)
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype)) if bias else None
+        self._dev_cache = {}
+
+    @torch.no_grad()
+    def quantize(self, weight_fp: torch.Tensor):
+        """Quantize ``weight_fp [out, in]`` per output feature (INT8, symmetric) into the buffers.
+
+        With ``handle_outliers`` the columns whose peak magnitude exceeds ``outlier_threshold`` are
+        kept aside in their original dtype (``outlier_weights``), only the remaining columns are
+        quantized, and ``int8_weights`` becomes ``[out, in - n_outliers]``.  The weight is moved
+        to the GPU for the kernel; its row length in bytes must be a multiple of 16.
+        """
+        self._dev_cache = {}
+        if self.handle_outliers:
+            w_normal, w_outlier, normal_cols, outlier_cols = separate_outliers(weight_fp, threshold=self.outlier_threshold)
+            self.outlier_weights = w_outlier
+            self.normal_cols = torch.tensor(normal_cols, dtype=torch.long)
+            self.outlier_cols = torch.tensor(outlier_cols, dtype=torch.long)
+            qt = quantize_tensor(w_normal.cuda().contiguous(), scheme="symmetric", dtype=torch.int8, mode="channel",
+                                 ch_axis=0)
+            self.int8_weights = qt.data
+        else:
+            qt = quantize_tensor(weight_fp.cuda().contiguous(), scheme="symmetric", dtype=torch.int8, mode="channel",
+                                 ch_axis=0)
+            self.int8_weights.copy_(qt.data)
+
+        assert torch.allclose(qt.zero_point, torch.zeros_like(qt.zero_point)), "Expect symmetric zp=0"
+        scale_1d = qt.scale.squeeze()
+        assert scale_1d.ndim == 1 and scale_1d.numel() == self.out_features
+        self.scales.copy_(scale_1d.to(self.scales.dtype))
+
+    def _on(self, name: str, dev: torch.device, dtype=None) -> torch.Tensor:
+        """Buffer ``name`` on ``dev`` (and cast to ``dtype``), cached while the buffer object is unchanged."""
+        src = getattr(self, name)
+        if src.device == dev and (dtype is None or src.dtype == dtype) and src.is_contiguous():
+            return src
+        key = (name, dev, dtype)
+        hit = self._dev_cache.get(key)
+        if hit is not None and hit[0] is src and hit[1] == src._version:
+            return hit[2]
+        moved = src.to(device=dev, dtype=dtype if dtype is not None else src.dtype).contiguous()
+        self._dev_cache[key] = (src, src._version, moved)
+        return moved
+
+    def forward(self, x: torch.Tensor):
+        """``y = x @ dequant(W).T (+ outlier columns in 16-bit) (+ bias)`` on the GPU, shape ``[..., out]``."""
+        if not x.is_cuda:
+            raise ValueError(
+                f"cuBladeW8A16LinearLayer.forward: input must be on CUDA, got device={x.device} "
+                "(this build has no CPU path)"
+            )
+        lead = x.shape[:-1]
+        x2d = x.reshape(-1, self.in_features)
+        if x2d.stride(-1) != 1:
+            x2d = x2d.contiguous()
+        dev = x2d.device
+        wq = self._on("int8_weights", dev)
+        scales = self._on("scales", dev)
+        bias = None
+        if self.bias is not None:
+            bias = self.bias.detach()
+            if bias.device != dev:
+                bias = bias.to(dev)
+            bias = bias.contiguous()
+
+        if self.handle_outliers and self.outlier_cols is not None and len(self.outlier_cols) > 0:
+            normal_idx = self._on("normal_cols", dev)
+            outlier_idx = self._on("outlier_cols", dev)
+            w_out = self._on("outlier_weights", dev, x2d.dtype)
+            x_normal = gather_columns(x2d, normal_idx)
+            x_out = gather_columns(x2d, outlier_idx)
+            y2d = w8a16_linear(x_normal, wq, scales, bias, x_out, w_out)
+        else:
+            y2d = w8a16_linear(x2d, wq, scales, bias)
+        return y2d.view(*lead, self.out_features)
+
+
+# BASELINE spelling (lower-case b) of the same class
+cubladeW8A16LinearLayer = cuBladeW8A16LinearLayer

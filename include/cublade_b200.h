@@ -1,0 +1,145 @@
+/*
+ * cublade_b200 -- C ABI of the B200 (sm_100a) quantization hot path.
+ *
+ * One shared library, libcublade_b200.so, no torch / pybind types in any
+ * signature: plain device pointers, sizes, a dtype code and a CUDA stream
+ * handle (cudaStream_t passed as void*).  Every entry point
+ *   - works on the CUDA device that is current on the calling thread,
+ *   - enqueues on `stream` and returns without synchronising,
+ *   - allocates nothing: outputs and scratch are the caller's
+ *     (exception: none -- cb_*_workspace_bytes tell the caller what to bring),
+ *   - returns CB_OK (0) or a cb_status error; cb_last_error() then holds text.
+ *
+ * Each entry point names the reference interface it stands in for, as
+ * <file>:<line> inside the emre570/cublade source tree.
+ */
+#ifndef CUBLADE_B200_H_
+#define CUBLADE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum cb_status {
+    CB_OK = 0,
+    CB_ERR_ARGUMENT = 1,    /* null pointer, negative size, bad enum          */
+    CB_ERR_DTYPE = 2,       /* dtype not accepted by this op                  */
+    CB_ERR_ALIGNMENT = 3,   /* reference-mandated alignment rule violated     */
+    CB_ERR_RANGE = 4,       /* size outside the supported range               */
+    CB_ERR_CUDA = 5,        /* a CUDA call or launch failed                   */
+    CB_ERR_WORKSPACE = 6,   /* workspace missing or too small                 */
+    CB_ERR_UNSUPPORTED = 7  /* valid request this build cannot serve          */
+} cb_status;
+
+/* element type of floating tensors */
+typedef enum cb_dtype { CB_F16 = 0, CB_BF16 = 1, CB_F32 = 2 } cb_dtype;
+
+/* library version: major*10000 + minor*100 + patch */
+int32_t cb_version(void);
+/* text of the last error raised on the calling thread ("" if none) */
+const char* cb_last_error(void);
+/* number of kernels this library has launched in the calling process */
+int64_t cb_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * Per-tensor FP8 E4M3.
+ * replaces quantize_per_tensor_fp8(x, eps) -> (q, scale)
+ *   cublade/kernels/cuda/quantization/quantize_per_tensor_fp8.cu:162-188
+ *   (binding cublade/bindings/cuda/quantize_fp8.py:15-34)
+ * x: n elements of CB_F16 / CB_BF16.  q: n bytes (e4m3 codes).  scale: fp32[1].
+ * amax_scratch: fp32[1] device scratch, overwritten.
+ * scale = 1 / (448 / max(amax, eps)); q = e4m3_rn_satfinite(float(x) * (448 / max(amax, eps))).
+ * ------------------------------------------------------------------------ */
+int32_t cb_quantize_per_tensor_fp8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
+                                   float* amax_scratch, void* stream);
+
+/* replaces dequantize_per_tensor_fp8(q, scale, out_dtype) -> y
+ *   cublade/kernels/cuda/quantization/dequantize_per_tensor_fp8.cu:84-115
+ *   (binding cublade/bindings/cuda/dequantize_fp8.py:15-35)
+ * y = out_dtype_rn(float(q) * scale[0]); out_dtype CB_F16 / CB_BF16. */
+int32_t cb_dequantize_per_tensor_fp8(const void* q, const float* scale, int64_t n, int32_t out_dtype, void* y,
+                                     void* stream);
+
+/* ------------------------------------------------------------------------
+ * INT8, symmetric, codes in [-127, 127].
+ * inv = fp32(127 / max(amax, eps)); q = clamp(rint(float(x) * inv)); scale = fp32(1 / inv).
+ * ------------------------------------------------------------------------ */
+/* replaces quantize_per_tensor_int8(x, eps)
+ *   cublade/kernels/cuda/quantization/quantize_int8.cu:470-484 (binding quantize_int8.py:18-38)
+ * x: CB_F16 / CB_BF16 / CB_F32. */
+int32_t cb_quantize_per_tensor_int8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
+                                    float* amax_scratch, void* stream);
+
+/* replaces quantize_per_channel_int8(x, eps): x viewed as [C, F], one scale per row
+ *   cublade/kernels/cuda/quantization/quantize_int8.cu:487-509 (binding quantize_int8.py:41-62)
+ * Like the reference, rejects F * sizeof(element) % 16 != 0 with CB_ERR_ALIGNMENT. scale: fp32[C]. */
+int32_t cb_quantize_per_channel_int8(const void* x, int32_t dtype, int64_t C, int64_t F, float eps, void* q,
+                                     float* scale, void* stream);
+
+/* replaces quantize_per_group_int8(x_grouped, group_size, eps): x is [num_groups, group_size]
+ *   cublade/kernels/cuda/quantization/quantize_int8.cu:514-536 (binding quantize_int8.py:65-87)
+ * group_size in (0, 4096] else CB_ERR_RANGE.  scale: fp32[num_groups]. */
+int32_t cb_quantize_per_group_int8(const void* x, int32_t dtype, int64_t num_groups, int64_t group_size, float eps,
+                                   void* q, float* scale, void* stream);
+
+/* replaces dequantize_per_tensor_int8(q, scale, out_dtype)
+ *   cublade/kernels/cuda/quantization/dequantize_int8.cu:210-224 (binding dequantize_int8.py:18-38) */
+int32_t cb_dequantize_per_tensor_int8(const void* q, const float* scale, int64_t n, int32_t out_dtype, void* y,
+                                      void* stream);
+
+/* replaces dequantize_per_channel_int8(q, scale, out_dtype): q is [C, F], scale fp32[C]
+ *   cublade/kernels/cuda/quantization/dequantize_int8.cu:226-247 (binding dequantize_int8.py:41-58)
+ * Like the reference, rejects F % 8 != 0 with CB_ERR_ALIGNMENT. */
+int32_t cb_dequantize_per_channel_int8(const void* q, const float* scale, int64_t C, int64_t F, int32_t out_dtype,
+                                       void* y, void* stream);
+
+/* replaces dequantize_per_group_int8(q_grouped, scale, group_size, out_dtype)
+ *   cublade/kernels/cuda/quantization/dequantize_int8.cu:249-273 (binding dequantize_int8.py:61-79) */
+int32_t cb_dequantize_per_group_int8(const void* q, const float* scale, int64_t num_groups, int64_t group_size,
+                                     int32_t out_dtype, void* y, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Split-phase per-tensor quantization, for tensors sharded over several GPUs:
+ * every rank runs cb_amax_abs on its shard, the caller max-reduces the fp32
+ * value across ranks, every rank runs cb_cast_per_tensor with the global amax.
+ * The two phases are the two kernels of the reference's single call
+ *   cublade/kernels/cuda/quantization/quantize_per_tensor_fp8.cu:140-159
+ *   cublade/kernels/cuda/quantization/quantize_int8.cu:394-410
+ * cb_amax_abs: amax[0] = max(amax[0], max|x|); the caller zeroes amax first.
+ * cb_cast_per_tensor: code_kind 0 = int8, 1 = e4m3.
+ * ------------------------------------------------------------------------ */
+int32_t cb_amax_abs(const void* x, int32_t dtype, int64_t n, float* amax, void* stream);
+int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float* amax, float eps, int32_t code_kind,
+                           void* q, float* scale, void* stream);
+
+/* ------------------------------------------------------------------------
+ * W8A16 linear:  y[m, n] = (sum_k x[m, k] * wq[n, k]) * scales[n]
+ *                          (+ sum_j xo[m, j] * wo[n, j])  (+ bias[n])
+ * replaces the forward of cuBladeW8A16LinearLayer
+ *   cublade/quantization/linear.py:83-137 and the Triton GEMM it calls
+ *   cublade/bindings/triton/matmul.py:17-132, cublade/kernels/triton/matmul_kernel.py:9-99
+ * x [M, K] and y [M, N] are CB_BF16 or CB_F16 (act_dtype), rows ldx / ldy
+ * elements apart.  wq [N, K] int8 row-major.  scales [N] of scales_dtype.
+ * bias [N] of bias_dtype or NULL.  xo [M, KO] / wo [N, KO] (act_dtype, KO may
+ * be 0 with NULL pointers) carry the LLM.int8 outlier columns kept in 16-bit.
+ * fp32 accumulation, one rounding to act_dtype at the end.
+ * path: 0 auto, 1 weight-streaming kernel, 2 tcgen05 tensor-core kernel.
+ * ------------------------------------------------------------------------ */
+size_t cb_w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int32_t cb_w8a16_linear(const void* x, int64_t M, int64_t K, int64_t ldx, const void* wq, int64_t N,
+                        const void* scales, int32_t scales_dtype, const void* bias, int32_t bias_dtype,
+                        const void* xo, int64_t ldxo, const void* wo, int64_t KO, void* y, int64_t ldy,
+                        int32_t act_dtype, void* workspace, size_t workspace_bytes, int32_t path, void* stream);
+
+/* dst[m, j] = src[m, cols[j]]: re-packs activation columns for the outlier split
+ * (the two fancy-index gathers of cublade/quantization/linear.py:101-102). elem_size 2 or 4. */
+int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols, void* dst,
+                          int64_t ld_dst, int32_t elem_size, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUBLADE_B200_H_ */

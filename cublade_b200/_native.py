@@ -104,3 +104,22 @@ def launch_count() -> int:
 
 def ptr(t):
     return None if t is None else t.data_ptr()
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(t: torch.Tensor):
+    """Context manager that makes ``t``'s device current; free when it already is."""
+    idx = t.device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(idx)

@@ -18,7 +18,7 @@ def dequantize_per_tensor_fp8(q: torch.Tensor, scale: torch.Tensor, dtype: torch
     """
     check_dequant_input(q, scale, dtype, torch.float8_e4m3fn, "torch.float8_e4m3fn")
     require(scale.numel() == 1, "scale must be a 0-d or 1-element tensor")
-    with torch.cuda.device(q.device):
+    with N.device_guard(q):
         y = torch.empty(q.shape, dtype=dtype, device=q.device)
         N.check(N.lib().cb_dequantize_per_tensor_fp8(q.data_ptr(), scale.data_ptr(), q.numel(), N.dtype_code(dtype),
                                                      y.data_ptr(), N.stream_ptr(q)))

@@ -12,7 +12,7 @@ from ._common import check_dequant_input, require
 def dequantize_per_tensor_int8(q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     check_dequant_input(q, scale, dtype, torch.int8, "torch.int8")
     require(scale.numel() == 1, "scale must be a scalar for per-tensor mode")
-    with torch.cuda.device(q.device):
+    with N.device_guard(q):
         y = torch.empty(q.shape, dtype=dtype, device=q.device)
         N.check(N.lib().cb_dequantize_per_tensor_int8(q.data_ptr(), scale.data_ptr(), q.numel(), N.dtype_code(dtype),
                                                       y.data_ptr(), N.stream_ptr(q)))
@@ -26,7 +26,7 @@ def dequantize_per_channel_int8(q: torch.Tensor, scale: torch.Tensor, dtype: tor
     C = q.size(0)
     F = q.numel() // C if C > 0 else 0
     require(scale.numel() == C, "scale must have C elements (size(0) of q)")
-    with torch.cuda.device(q.device):
+    with N.device_guard(q):
         y = torch.empty(q.shape, dtype=dtype, device=q.device)
         N.check(N.lib().cb_dequantize_per_channel_int8(q.data_ptr(), scale.data_ptr(), C, F, N.dtype_code(dtype),
                                                        y.data_ptr(), N.stream_ptr(q)))
@@ -41,7 +41,7 @@ def dequantize_per_group_int8(q_grouped: torch.Tensor, scale: torch.Tensor, grou
     require(0 < group_size <= 4096, "group_size must be in (0, 4096]")
     G = q_grouped.size(0)
     require(scale.numel() == G, "scale must have num_groups elements")
-    with torch.cuda.device(q_grouped.device):
+    with N.device_guard(q_grouped):
         y = torch.empty(q_grouped.shape, dtype=dtype, device=q_grouped.device)
         N.check(N.lib().cb_dequantize_per_group_int8(q_grouped.data_ptr(), scale.data_ptr(), G, int(group_size),
                                                      N.dtype_code(dtype), y.data_ptr(), N.stream_ptr(q_grouped)))

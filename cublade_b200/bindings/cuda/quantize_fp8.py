@@ -23,7 +23,7 @@ def quantize_per_tensor_fp8(x: torch.Tensor, eps: float = 1e-12) -> tuple[torch.
         ``(q, scale)``: ``q`` float8_e4m3fn with x's shape, ``scale`` 0-d float32.
     """
     check_quant_input(x, (torch.float16, torch.bfloat16), "torch.float16 or torch.bfloat16")
-    with torch.cuda.device(x.device):
+    with N.device_guard(x):
         q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
         scale = torch.empty((), dtype=torch.float32, device=x.device)
         amax = torch.empty((), dtype=torch.float32, device=x.device)

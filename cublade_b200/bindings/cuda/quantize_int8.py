@@ -19,7 +19,7 @@ _TEXT = "torch.float16, torch.bfloat16, or torch.float32"
 def quantize_per_tensor_int8(x: torch.Tensor, eps: float = 1e-12) -> tuple[torch.Tensor, torch.Tensor]:
     """One scale for the whole tensor. Returns ``(q int8 like x, scale 0-d float32)``."""
     check_quant_input(x, _ALLOWED, _TEXT)
-    with torch.cuda.device(x.device):
+    with N.device_guard(x):
         q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
         scale = torch.empty((), dtype=torch.float32, device=x.device)
         amax = torch.empty((), dtype=torch.float32, device=x.device)
@@ -35,7 +35,7 @@ def quantize_per_channel_int8(x: torch.Tensor, eps: float = 1e-12) -> tuple[torc
     require(x.dim() >= 1, "x must have at least 1 dim for per-channel quant")
     C = x.size(0)
     F = x.numel() // C if C > 0 else 0
-    with torch.cuda.device(x.device):
+    with N.device_guard(x):
         q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
         scale = torch.empty((C,), dtype=torch.float32, device=x.device)
         N.check(N.lib().cb_quantize_per_channel_int8(x.data_ptr(), N.dtype_code(x.dtype), C, F, float(eps),
@@ -51,7 +51,7 @@ def quantize_per_group_int8(x_grouped: torch.Tensor, group_size: int, eps: float
     require(x_grouped.size(1) == group_size, "x_grouped.size(1) must equal group_size")
     require(0 < group_size <= 4096, "group_size must be in (0, 4096]")
     G = x_grouped.size(0)
-    with torch.cuda.device(x_grouped.device):
+    with N.device_guard(x_grouped):
         q = torch.empty(x_grouped.shape, dtype=torch.int8, device=x_grouped.device)
         scale = torch.empty((G,), dtype=torch.float32, device=x_grouped.device)
         N.check(N.lib().cb_quantize_per_group_int8(x_grouped.data_ptr(), N.dtype_code(x_grouped.dtype), G,

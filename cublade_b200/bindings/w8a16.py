@@ -28,7 +28,7 @@ def gather_columns(src: torch.Tensor, cols: torch.Tensor, ld_dst: Optional[int] 
         raise ValueError("gather_columns: src and cols (int64) must be CUDA tensors")
     M, n = src.shape[0], cols.numel()
     ld = ld_dst if ld_dst is not None else (n + 7) // 8 * 8
-    with torch.cuda.device(src.device):
+    with N.device_guard(src):
         buf = torch.empty((M, max(ld, 1)), dtype=src.dtype, device=src.device)
         N.check(N.lib().cb_gather_columns(src.data_ptr(), M, src.stride(0), cols.data_ptr(), n, buf.data_ptr(),
                                           buf.stride(0), src.element_size(), N.stream_ptr(src)))
@@ -86,7 +86,7 @@ def w8a16_linear(
                 or x_outlier.dtype != x2d.dtype or w_outlier.dtype != x2d.dtype):
             raise ValueError("w8a16_linear: outlier operands must be [M, KO] / contiguous [N, KO] in the activation dtype")
     L = N.lib()
-    with torch.cuda.device(dev):
+    with N.device_guard(x2d):
         y = out if out is not None else torch.empty((M, Nout), dtype=x2d.dtype, device=dev)
         ws_bytes = int(L.cb_w8a16_workspace_bytes(M, Nout, K))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None

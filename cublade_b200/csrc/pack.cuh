@@ -111,16 +111,52 @@ __device__ __forceinline__ void pack_to_floats(const uint4& raw, float (&f)[DTyp
     }
 }
 
-// max |lane| of a pack, NaN lanes dropped (fmaxf returns the non-NaN operand).
+// Running max |lane|, NaN lanes dropped (both fmaxf and __hmax2 return the non-NaN operand).
+// 16-bit types keep a packed pair of running maxima and compare two lanes per instruction:
+// clearing the sign bits is one AND, the max is one packed min/max instruction.
 template <typename T>
-__device__ __forceinline__ float pack_absmax(const uint4& raw, float running) {
-    constexpr int L = DTypeTraits<T>::kLanes;
-    float f[L];
-    pack_to_floats<T>(raw, f);
-#pragma unroll
-    for (int k = 0; k < L; ++k) running = fmaxf(running, fabsf(f[k]));
-    return running;
-}
+struct AbsMax;
+
+template <>
+struct AbsMax<float> {
+    float m = 0.0f;
+    __device__ __forceinline__ void update(const uint4& raw) {
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(raw.x)), fabsf(__uint_as_float(raw.y))),
+                           fmaxf(fabsf(__uint_as_float(raw.z)), fabsf(__uint_as_float(raw.w)))));
+    }
+    __device__ __forceinline__ void update1(float v) { m = fmaxf(m, fabsf(v)); }
+    __device__ __forceinline__ float finish() const { return m; }
+};
+
+template <>
+struct AbsMax<__nv_bfloat16> {
+    __nv_bfloat162 m2 = __nv_bfloat162(__ushort_as_bfloat16(0), __ushort_as_bfloat16(0));
+    float m1 = 0.0f;
+    __device__ __forceinline__ void word(uint32_t w) {
+        w &= 0x7fff7fffu;
+        m2 = __hmax2(m2, *reinterpret_cast<const __nv_bfloat162*>(&w));
+    }
+    __device__ __forceinline__ void update(const uint4& raw) { word(raw.x); word(raw.y); word(raw.z); word(raw.w); }
+    __device__ __forceinline__ void update1(float v) { m1 = fmaxf(m1, fabsf(v)); }
+    __device__ __forceinline__ float finish() const {
+        return fmaxf(m1, fmaxf(__bfloat162float(__low2bfloat16(m2)), __bfloat162float(__high2bfloat16(m2))));
+    }
+};
+
+template <>
+struct AbsMax<__half> {
+    __half2 m2 = __half2(__ushort_as_half(0), __ushort_as_half(0));
+    float m1 = 0.0f;
+    __device__ __forceinline__ void word(uint32_t w) {
+        w &= 0x7fff7fffu;
+        m2 = __hmax2(m2, *reinterpret_cast<const __half2*>(&w));
+    }
+    __device__ __forceinline__ void update(const uint4& raw) { word(raw.x); word(raw.y); word(raw.z); word(raw.w); }
+    __device__ __forceinline__ void update1(float v) { m1 = fmaxf(m1, fabsf(v)); }
+    __device__ __forceinline__ float finish() const {
+        return fmaxf(m1, fmaxf(__half2float(__low2half(m2)), __half2float(__high2half(m2))));
+    }
+};
 
 // Warp-shuffle max over WIDTH adjacent lanes (WIDTH a power of two <= 32).
 template <int WIDTH>
@@ -153,25 +189,41 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t c) {
 // ---------------------------------------------------------------------------
 // Whole-pack conversions.  Code kinds.
 // ---------------------------------------------------------------------------
-struct Int8Code {
+// d = (c << 16) | (sat_s8(a) << 8) | sat_s8(b)
+__device__ __forceinline__ uint32_t cvt_pack_s8(int a, int b, uint32_t c) {
+    uint32_t d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// CLAMP_LOW: also clamp at -127.  When the multiplier is 127 / max(amax, eps) with amax the true
+// maximum of the data, |x * inv| <= 127 * (1 + 2^-24)^2 < 127.5, so the rounded value is already
+// inside [-127, 127] (NaN converts to 0) and the saturating pack alone reproduces the reference's
+// clamp; a caller-supplied amax (split-phase entry point) needs the explicit lower clamp.
+template <bool CLAMP_LOW>
+struct Int8CodeT {
     static constexpr float kQmax = kInt8Qmax;
     __device__ __forceinline__ static uint32_t encode4(float a, float b, float c, float d) {
-        const uint32_t x = (uint32_t)round_half_even_clamp_int8(a) & 0xffu;
-        const uint32_t y = (uint32_t)round_half_even_clamp_int8(b) & 0xffu;
-        const uint32_t z = (uint32_t)round_half_even_clamp_int8(c) & 0xffu;
-        const uint32_t w = (uint32_t)round_half_even_clamp_int8(d);
-        return x | (y << 8) | (z << 16) | (w << 24);
+        int ia = __float2int_rn(a), ib = __float2int_rn(b), ic = __float2int_rn(c), id = __float2int_rn(d);
+        if constexpr (CLAMP_LOW) {
+            ia = max(ia, -127); ib = max(ib, -127); ic = max(ic, -127); id = max(id, -127);
+        }
+        return cvt_pack_s8(ib, ia, cvt_pack_s8(id, ic, 0u));
     }
     __device__ __forceinline__ static uint8_t encode1(float a) { return (uint8_t)round_half_even_clamp_int8(a); }
-    // four codes in one word -> four fp32
+    // four codes in one word -> four fp32, exactly: the byte (biased by 128) is dropped into the
+    // mantissa of 2^23 and the bias subtracted, one permute and one add per lane.
     __device__ __forceinline__ static void decode4(uint32_t w, float (&f)[4]) {
-        f[0] = (float)(int)(int8_t)(w & 0xffu);
-        f[1] = (float)(int)(int8_t)((w >> 8) & 0xffu);
-        f[2] = (float)(int)(int8_t)((w >> 16) & 0xffu);
-        f[3] = (float)((int)w >> 24);
+        const uint32_t u = w ^ 0x80808080u;
+        f[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+        f[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+        f[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+        f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
     }
     __device__ __forceinline__ static float decode1(uint8_t c) { return (float)(int)(int8_t)c; }
 };
+using Int8Code = Int8CodeT<false>;
+using Int8CodeClamped = Int8CodeT<true>;
 
 struct E4M3Code {
     static constexpr float kQmax = kE4M3Qmax;

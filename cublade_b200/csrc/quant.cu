@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
     const int64_t npk = n / E;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
     const uint4* xp = reinterpret_cast<const uint4*>(x);
-    float m = 0.0f;
+    AbsMax<T> am;
     for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const int64_t p0 = c * kChunkPacks + threadIdx.x;
         if (p0 + 3 * kBlock < npk) {
@@ -69,25 +69,25 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
             uint4 v1 = ld_keep16(xp + p0 + kBlock);
             uint4 v2 = ld_keep16(xp + p0 + 2 * kBlock);
             uint4 v3 = ld_keep16(xp + p0 + 3 * kBlock);
-            m = pack_absmax<T>(v0, m);
-            m = pack_absmax<T>(v1, m);
-            m = pack_absmax<T>(v2, m);
-            m = pack_absmax<T>(v3, m);
+            am.update(v0);
+            am.update(v1);
+            am.update(v2);
+            am.update(v3);
         } else {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const int64_t p = p0 + k * kBlock;
-                if (p < npk) m = pack_absmax<T>(ld_keep16(xp + p), m);
+                if (p < npk) am.update(ld_keep16(xp + p));
             }
         }
     }
     // ragged tail (< one pack), CTA 0
     if (blockIdx.x == 0) {
         const int64_t t = npk * E + threadIdx.x;
-        if (t < n) m = fmaxf(m, fabsf(DTypeTraits<T>::to_float(x[t])));
+        if (t < n) am.update1(DTypeTraits<T>::to_float(x[t]));
     }
     __shared__ float red[kBlock / 32];
-    m = block_max(m, red);
+    float m = block_max(am.finish(), red);
     if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
 }
 
@@ -161,27 +161,28 @@ __global__ void __launch_bounds__(kBlock) cast_tensor_scalar_kernel(const T* __r
 // Needs L % lanes == 0 and 16-byte aligned x, L*PACKS... checked by the launcher.
 // (reference: quantize_int8.cu:173-297 per-channel, :307-371 per-group)
 // ===========================================================================
-template <typename T, typename Code, int TEAM, int PACKS>
-__global__ void __launch_bounds__(kBlock) quant_segments_kernel(const T* __restrict__ x, int64_t nseg, int npk,
+template <typename T, typename Code, int TEAM, int PACKS, int BLOCK>
+__global__ void __launch_bounds__(BLOCK) quant_segments_kernel(const T* __restrict__ x, int64_t nseg, int npk,
                                                                 float eps, uint8_t* __restrict__ q,
                                                                 float* __restrict__ scale_out) {
     constexpr int E = DTypeTraits<T>::kLanes;
-    constexpr int kTeamsPerCta = kBlock / TEAM;
+    constexpr int kTeamsPerCta = BLOCK / TEAM;
     const int t = threadIdx.x % TEAM;
     const int64_t seg = (int64_t)blockIdx.x * kTeamsPerCta + threadIdx.x / TEAM;
     const bool live = seg < nseg;
     const uint4* xp = reinterpret_cast<const uint4*>(x) + seg * (int64_t)npk;
 
     uint4 v[PACKS];
-    float m = 0.0f;
 #pragma unroll
     for (int k = 0; k < PACKS; ++k) {
         const int p = t + k * TEAM;
         if (live && p < npk) v[k] = ld_stream16(xp + p);
         else v[k] = make_uint4(0u, 0u, 0u, 0u);
     }
+    AbsMax<T> am;
 #pragma unroll
-    for (int k = 0; k < PACKS; ++k) m = pack_absmax<T>(v[k], m);
+    for (int k = 0; k < PACKS; ++k) am.update(v[k]);
+    float m = am.finish();
 
     if constexpr (TEAM <= 32) {
         m = team_max<TEAM>(m);
@@ -213,10 +214,10 @@ __global__ void __launch_bounds__(kBlock) quant_long_rows_kernel(const T* __rest
     constexpr int E = DTypeTraits<T>::kLanes;
     const int64_t seg = blockIdx.x;
     const uint4* xp = reinterpret_cast<const uint4*>(x) + seg * npk;
-    float m = 0.0f;
-    for (int64_t p = threadIdx.x; p < npk; p += kBlock) m = pack_absmax<T>(ld_keep16(xp + p), m);
+    AbsMax<T> am;
+    for (int64_t p = threadIdx.x; p < npk; p += kBlock) am.update(ld_keep16(xp + p));
     __shared__ float red[kBlock / 32];
-    m = block_max(m, red);
+    const float m = block_max(am.finish(), red);
     const InvScale is = inv_and_scale<Code>(m, eps);
     if (threadIdx.x == 0) scale_out[seg] = is.scale;
     uint8_t* qp = q + seg * npk * E;
@@ -365,9 +366,9 @@ cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float*
         }
     } else if (code == kCodeInt8) {
         switch (dtype) {
-            case kF16: return cast_tensor_t<__half, Int8Code>(x, n, amax, eps, q, scale_out, s);
-            case kBF16: return cast_tensor_t<__nv_bfloat16, Int8Code>(x, n, amax, eps, q, scale_out, s);
-            case kF32: return cast_tensor_t<float, Int8Code>(x, n, amax, eps, q, scale_out, s);
+            case kF16: return cast_tensor_t<__half, Int8CodeClamped>(x, n, amax, eps, q, scale_out, s);
+            case kBF16: return cast_tensor_t<__nv_bfloat16, Int8CodeClamped>(x, n, amax, eps, q, scale_out, s);
+            case kF32: return cast_tensor_t<float, Int8CodeClamped>(x, n, amax, eps, q, scale_out, s);
         }
     }
     return cudaErrorInvalidValue;
@@ -375,9 +376,11 @@ cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float*
 
 template <typename T, typename Code, int TEAM, int PACKS>
 static void seg_launch(const void* x, int64_t nseg, int npk, float eps, void* q, float* scale_out, cudaStream_t s) {
-    constexpr int kTeamsPerCta = kBlock / TEAM;
+    // sub-warp teams share a 256-thread CTA; a CTA-wide team is its own CTA
+    constexpr int BLOCK = TEAM > 32 ? TEAM : kBlock;
+    constexpr int kTeamsPerCta = BLOCK / TEAM;
     const int64_t grid = (nseg + kTeamsPerCta - 1) / kTeamsPerCta;
-    quant_segments_kernel<T, Code, TEAM, PACKS><<<(unsigned)grid, kBlock, 0, s>>>(
+    quant_segments_kernel<T, Code, TEAM, PACKS, BLOCK><<<(unsigned)grid, BLOCK, 0, s>>>(
         static_cast<const T*>(x), nseg, npk, eps, static_cast<uint8_t*>(q), scale_out);
 }
 
@@ -388,7 +391,7 @@ static void seg_pick_packs(int packs, const void* x, int64_t nseg, int npk, floa
     else if (packs <= 2) seg_launch<T, Code, TEAM, 2>(x, nseg, npk, eps, q, sc, s);
     else if (packs <= 4) seg_launch<T, Code, TEAM, 4>(x, nseg, npk, eps, q, sc, s);
     else {
-        if constexpr (TEAM == kBlock) seg_launch<T, Code, TEAM, 8>(x, nseg, npk, eps, q, sc, s);
+        if constexpr (TEAM > 32) seg_launch<T, Code, TEAM, 8>(x, nseg, npk, eps, q, sc, s);
     }
 }
 

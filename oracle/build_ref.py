@@ -71,7 +71,13 @@ def load_ref(name: str):
     """Import a prebuilt reference extension from ``oracle/_ref`` (never rebuilds)."""
     import importlib.util
 
-    import torch  # noqa: F401  (libtorch must be loaded before the extension)
+    import torch  # libtorch must be loaded before the extension
+
+    # Loading these extensions before the CUDA context exists crashed the first CUDA call on
+    # the GPU box, so bring the context up first.
+    if torch.cuda.is_available():
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")
 
     so = OUT / name / f"{name}.so"
     if not so.exists():

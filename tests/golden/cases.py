@@ -1,0 +1,57 @@
+"""Seeded small inputs shared by the golden-vector generators and the tests that replay them.
+
+The shapes are the ones the reference's demo scripts exercise
+(examples/quantization/quant_dequant_fp8.py:48-58, quant_dequant_int8.py:51-91) plus ragged
+sizes that reach the kernels' tail paths.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def _g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def fp8_cases():
+    bf, hf = torch.bfloat16, torch.float16
+    single = torch.full((10_000,), 0.01, dtype=bf)
+    single[5000] = 99.5
+    return {
+        "fp8_toy_1_to_8": torch.arange(1, 9, dtype=bf),
+        "fp8_single_outlier": single,
+        "fp8_tail_2049": torch.randn(2049, generator=_g(10)).to(bf),
+        "fp8_random_bf16": (torch.randn(16384, generator=_g(11)) * 3.0).to(bf),
+        "fp8_random_fp16": (torch.randn(16384, generator=_g(12)) * 3.0).to(hf),
+        "fp8_all_zero": torch.zeros(512, dtype=bf),
+        "fp8_small_magnitudes": (torch.randn(4096, generator=_g(13)) * 1e-3).to(bf),
+    }
+
+
+def int8_tensor_cases():
+    return {
+        "i8t_linspace": torch.linspace(-1, 1, 256).to(torch.bfloat16),
+        "i8t_tail_2049": torch.randn(2049, generator=_g(20)).to(torch.bfloat16),
+        "i8t_fp16": (torch.randn(8192, generator=_g(21)) * 3.0).to(torch.float16),
+        "i8t_fp32_4099": torch.randn(4099, generator=_g(22)),
+    }
+
+
+def int8_channel_cases():
+    return {
+        "i8c_8x1024": (torch.randn(8, 1024, generator=_g(30)) * 0.02).to(torch.bfloat16),
+        "i8c_64x1000_fp16": (torch.randn(64, 1000, generator=_g(31)) * 0.5).to(torch.float16),
+        "i8c_16x260_fp32": torch.randn(16, 260, generator=_g(32)) * 0.02,
+        "i8c_4x16384": (torch.randn(4, 16384, generator=_g(33)) * 0.02).to(torch.bfloat16),
+    }
+
+
+def int8_group_cases():
+    """name -> (grouped [num_groups, G] tensor, G)"""
+    return {
+        "i8g_1024_g32": ((torch.randn(32, 32, generator=_g(40)) * 2.0).to(torch.bfloat16), 32),
+        "i8g_64x256_g128": ((torch.randn(128, 128, generator=_g(41)) * 2.0).to(torch.bfloat16), 128),
+        "i8g_g5_scalar": ((torch.randn(256, 5, generator=_g(42)) * 2.0).to(torch.bfloat16), 5),
+        "i8g_g4096": ((torch.randn(3, 4096, generator=_g(43)) * 2.0).to(torch.float16), 4096),
+        "i8g_fp32_g16": (torch.randn(64, 16, generator=_g(44)), 16),
+    }

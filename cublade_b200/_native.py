@@ -44,6 +44,7 @@ SIGNATURES = {
     "cb_w8a16_linear": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int32, c_void_p,
                                    c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p,
                                    c_size_t, c_int32, c_void_p]),
+    "cb_device_error_state": (c_int32, [c_void_p, c_void_p]),
     "cb_gather_columns": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p]),
 }
 
@@ -100,6 +101,15 @@ def stream_ptr(t: torch.Tensor) -> int:
 
 def launch_count() -> int:
     return int(lib().cb_launch_count())
+
+
+def device_error_state(device=None) -> int:
+    """Synchronise the current stream and return the device's bounded-wait flag (0 = healthy)."""
+    flag = ctypes.c_uint32(0)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        check(lib().cb_device_error_state(ctypes.byref(flag), torch.cuda.current_stream(dev).cuda_stream))
+    return int(flag.value)
 
 
 def ptr(t):

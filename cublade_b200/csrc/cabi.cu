@@ -183,6 +183,15 @@ int32_t cb_w8a16_linear(const void* x, int64_t M, int64_t K, int64_t ldx, const 
     return cuda_result(e, "cb_w8a16_linear", 1);
 }
 
+int32_t cb_device_error_state(uint32_t* host_flag, void* stream) {
+    if (!host_flag) return fail(CB_ERR_ARGUMENT, "cb_device_error_state: null pointer");
+    unsigned int v = 0;
+    cudaError_t e = cb::w8a16_tc_read_error(&v, as_stream(stream));
+    if (e != cudaSuccess) return cuda_result(e, "cb_device_error_state", 0);
+    *host_flag = v;
+    return CB_OK;
+}
+
 int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols, void* dst,
                           int64_t ld_dst, int32_t elem_size, void* stream) {
     if (M < 0 || ncols < 0) return fail(CB_ERR_ARGUMENT, "cb_gather_columns: negative size");

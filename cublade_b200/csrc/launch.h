@@ -56,6 +56,9 @@ struct W8A16Args {
 size_t w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 // path: 0 = automatic, 1 = weight-streaming (skinny M) kernel, 2 = tcgen05 GEMM
 cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s);
+// reads (and leaves untouched) the per-device flag a kernel raises when one of its bounded waits
+// expired; synchronises the stream.
+cudaError_t w8a16_tc_read_error(unsigned int* host_value, cudaStream_t s);
 // gathers columns: dst[m, j] = src[m, cols[j]] (activation re-pack for the outlier split)
 cudaError_t launch_gather_cols(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
                                void* dst, int64_t ld_dst, int elem_size, cudaStream_t s);

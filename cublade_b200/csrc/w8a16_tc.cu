@@ -1,6 +1,583 @@
-// placeholder until the tcgen05 kernel lands
+// W8A16 linear for tall activations: a tcgen05 / TMEM GEMM fed by TMA that widens int8 weight
+// tiles to 16-bit floats in shared memory.
+//
+//   y[m, n] = (sum_k x[m, k] * wq[n, k]) * scale[n] + sum_j xo[m, j] * wo[n, j] + bias[n]
+//
+// Replaces the reference's per-call chain "cast the whole weight to bf16, transpose it, Triton
+// tl.dot GEMM, multiply by scales, add bias" (cublade/quantization/linear.py:123-135,
+// cublade/kernels/triton/matmul_kernel.py:9-99) with one persistent kernel.
+//
+// Orientation ("swap-AB"): the WEIGHT tile is the 128-row UMMA operand A and the ACTIVATION tile
+// is the (up to) 256-row operand B, so the accumulator in TMEM is D[n_local (lane), m_local
+// (column)].  Consequences: (1) the int8 -> 16-bit conversion work per flop is halved compared
+// with putting the weights on the 256 side; (2) the per-output-channel scale and bias are one
+// scalar per TMEM lane, i.e. per epilogue thread; (3) for a fixed column m the 32 lanes of an
+// epilogue warp store 32 consecutive n of y[m, :], a 64-byte contiguous segment.
+//
+// Warp roles in a CTA of 14 warps (one CTA per SM, persistent over output tiles):
+//   warp 0      TMA producer: x tile (bf16/f16, 128-byte swizzle) and int8 weight tile, per k-block
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128, N=tile_x, K=16) x4 per
+//               k-block and commits to the "slot free" / "accumulator ready" barriers; also owns
+//               the TMEM allocation (512 columns = two accumulators)
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, * scale, + outlier side product, + bias,
+//               round once, store; overlaps the next tile's main loop (double-buffered TMEM)
+//   warps 6-13  converters: int8 tile (shared) -> registers -> 16-bit in the canonical K-major
+//               128-byte-swizzled UMMA layout (shared), then fence.proxy.async + barrier arrive
+//
+// No TMA multicast, no clusters, no peer memory.  Every mbarrier wait is bounded: on expiry the
+// kernel raises an error flag in global memory, every role leaves its loop, TMEM is released and
+// the kernel returns.
+
 #include "launch.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdio>
+#include <mutex>
+
 namespace cb {
-bool w8a16_tc_supported(const W8A16Args&) { return false; }
-cudaError_t launch_w8a16_tc(const W8A16Args&, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int kTileN = 128;     // weight rows (output features) per tile = UMMA M
+constexpr int kBlockK = 64;     // k per pipeline stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int kMaxTileX = 256;  // activation rows per tile = UMMA N (multiple of 16)
+constexpr int kStagesX = 4;     // activation tiles in flight (32 KiB each at 256 rows)
+constexpr int kStagesA = 3;     // converted weight tiles (16 KiB each)
+constexpr int kStagesW8 = 4;    // int8 weight tiles (8 KiB each)
+constexpr int kConvWarps = 8;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = (2 + kEpiWarps + kConvWarps) * 32;
+constexpr int kTmemCols = 512;
+
+constexpr uint32_t kBytesX = kMaxTileX * kBlockK * 2;  // 32768
+constexpr uint32_t kBytesA = kTileN * kBlockK * 2;     // 16384
+constexpr uint32_t kBytesW8 = kTileN * kBlockK;        // 8192
+
+struct SmemLayout {
+    static constexpr uint32_t x = 0;
+    static constexpr uint32_t a = x + kStagesX * kBytesX;
+    static constexpr uint32_t w8 = a + kStagesA * kBytesA;
+    static constexpr uint32_t bars = w8 + kStagesW8 * kBytesW8;
+    // barriers: full_x[kStagesX], empty_x[kStagesX], full_w8, empty_w8, full_a, empty_a, tmem_full[2], tmem_empty[2]
+    static constexpr uint32_t n_bars = 2 * kStagesX + 2 * kStagesW8 + 2 * kStagesA + 4;
+    static constexpr uint32_t tmem_slot = bars + n_bars * 8;
+    static constexpr uint32_t abort_flag = tmem_slot + 4;
+    static constexpr uint32_t total = abort_flag + 4;
+};
+constexpr uint32_t kSmemBytes = SmemLayout::total + 1024;  // + slack to align the base to 1024 B
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait (about one second of SM clocks).  Returns false on expiry or when another role
+// has already raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 2000000000LL) {
+            *abort_flag = 1u;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes (64 16-bit
+// elements) in the 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), descriptor
+// version 1, layout type 2 (SWIZZLE_128B).  Advancing k by 16 elements adds 32 bytes to the
+// start address.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);   // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024u >> 4) << 32;               // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                          // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, A and B of the same 16-bit format, both
+// K-major, M = 128, N = tile_x.
+__device__ __forceinline__ uint32_t make_idesc(bool bf16, uint32_t n) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+}
+
+template <typename A>
+struct Widen;
+template <>
+struct Widen<__nv_bfloat16> {
+    static constexpr bool kBf16 = true;
+    // four int8 codes -> (c0,c1), (c2,c3) as bf16 pairs; exact (see w8a16_stream.cu)
+    __device__ __forceinline__ static void four(uint32_t c, uint32_t& lo, uint32_t& hi) {
+        const uint32_t u = c ^ 0x80808080u;
+        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+        lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+        hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+    }
+    __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct Widen<__half> {
+    static constexpr bool kBf16 = false;
+    __device__ __forceinline__ static void four(uint32_t c, uint32_t& lo, uint32_t& hi) {
+        const uint32_t u = c ^ 0x80808080u;
+        const uint32_t p0 = __byte_perm(u, 0x64006400u, 0x7150);
+        const uint32_t p1 = __byte_perm(u, 0x64006400u, 0x7352);
+        const __half2 k = __half2half2(__ushort_as_half((unsigned short)0x6480));
+        __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&p0), k);
+        __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&p1), k);
+        lo = *reinterpret_cast<uint32_t*>(&a);
+        hi = *reinterpret_cast<uint32_t*>(&b);
+    }
+    __device__ __forceinline__ static float to_float(__half v) { return __half2float(v); }
+    __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
+};
+
+__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
+    if (dtype == kF32) return static_cast<const float*>(p)[i];
+    if (dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+struct TcParams {
+    int64_t M, N, K;
+    const void* scales;
+    int scales_dtype;
+    const void* bias;
+    int bias_dtype;
+    const void* xo;  // [M, KO] 16-bit
+    const void* wo;  // [N, KO] 16-bit
+    int64_t KO, ldxo;
+    void* y;
+    int64_t ldy;
+    int tile_x;      // activation rows per tile (multiple of 16, <= 256)
+    int tiles_x;     // ceil(M / tile_x)
+    int tiles_n;     // ceil(N / 128)
+    unsigned int* error_flag;  // global; set to 1 when a bounded wait expired
+};
+
+constexpr int kMaxKO = 32;  // outlier columns handled by the epilogue's CUDA-core side product
+
+template <typename A>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte aligned base (the 128-byte swizzle pattern repeats every 1024 bytes)
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sx = base + SmemLayout::x, sa = base + SmemLayout::a, sw8 = base + SmemLayout::w8;
+    const uint32_t bars = base + SmemLayout::bars;
+    const uint32_t full_x = bars, empty_x = full_x + 8 * kStagesX;
+    const uint32_t full_w8 = empty_x + 8 * kStagesX, empty_w8 = full_w8 + 8 * kStagesW8;
+    const uint32_t full_a = empty_w8 + 8 * kStagesW8, empty_a = full_a + 8 * kStagesA;
+    const uint32_t tmem_full = empty_a + 8 * kStagesA, tmem_empty = tmem_full + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + SmemLayout::tmem_slot);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + SmemLayout::abort_flag);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (int)((p.K + kBlockK - 1) / kBlockK);
+    const int total_tiles = p.tiles_x * p.tiles_n;
+    const uint32_t x_bytes = (uint32_t)p.tile_x * kBlockK * 2;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStagesX; ++i) { mbar_init(full_x + 8 * i, 1); mbar_init(empty_x + 8 * i, 1); }
+        for (int i = 0; i < kStagesW8; ++i) { mbar_init(full_w8 + 8 * i, 1); mbar_init(empty_w8 + 8 * i, kConvWarps); }
+        for (int i = 0; i < kStagesA; ++i) { mbar_init(full_a + 8 * i, kConvWarps); mbar_init(empty_a + 8 * i, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tmem_full + 8 * i, 1); mbar_init(tmem_empty + 8 * i, kEpiWarps); }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&map_x);
+        prefetch_tmap(&map_w);
+    }
+    if (warp == 1) tmem_alloc(base + SmemLayout::tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t ix = 0, iw = 0;  // running k-block counters for the two rings
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int tx = t % p.tiles_x, tn = t / p.tiles_x;
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    {
+                        const uint32_t s = iw % kStagesW8, ph = (iw / kStagesW8) & 1u;
+                        ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
+                        tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, tn * kTileN, full_w8 + 8 * s);
+                        ++iw;
+                    }
+                    {
+                        const uint32_t s = ix % kStagesX, ph = (ix / kStagesX) & 1u;
+                        ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(full_x + 8 * s, x_bytes);
+                        tma_load_2d(sx + s * kBytesX, &map_x, kb * kBlockK, tx * p.tile_x, full_x + 8 * s);
+                        ++ix;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(Widen<A>::kBf16, (uint32_t)p.tile_x);
+            uint32_t ix = 0, ia = 0, it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+                const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+                ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const uint32_t s_a = ia % kStagesA, ph_a = (ia / kStagesA) & 1u;
+                    const uint32_t s_x = ix % kStagesX, ph_x = (ix / kStagesX) & 1u;
+                    ok = mbar_wait(full_a + 8 * s_a, ph_a, abort_flag) && mbar_wait(full_x + 8 * s_x, ph_x, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t adesc = make_kmajor_sw128_desc(sa + s_a * kBytesA);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(sx + s_x * kBytesX);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        // +32 bytes per 16-element k step: +2 in the (>>4) start-address field
+                        umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_a + 8 * s_a);  // both operand slots are free once these MMAs retire
+                    umma_commit(empty_x + 8 * s_x);
+                    ++ia;
+                    ++ix;
+                }
+                if (!ok) break;
+                umma_commit(tmem_full + 8 * acc);  // accumulator complete -> epilogue
+            }
+        }
+    } else if (warp < 2 + kEpiWarps) {
+        // ------------------------------ epilogue ------------------------------
+        const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
+        const A* xo = static_cast<const A*>(p.xo);
+        const A* wo = static_cast<const A*>(p.wo);
+        A* y = static_cast<A*>(p.y);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+            const int tx = t % p.tiles_x, tn = t / p.tiles_x;
+            const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+            const int64_t n = (int64_t)tn * kTileN + quarter * 32 + lane;
+            const bool n_ok = n < p.N;
+            const float scale = n_ok ? load_scalar(p.scales, p.scales_dtype, n) : 0.0f;
+            const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+            float wo_row[kMaxKO];
+            if (p.KO > 0) {
+#pragma unroll
+                for (int j = 0; j < kMaxKO; ++j)
+                    wo_row[j] = (n_ok && j < p.KO) ? Widen<A>::to_float(wo[n * p.KO + j]) : 0.0f;
+            }
+            ok = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t m_base = (int64_t)tx * p.tile_x;
+            for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX + (uint32_t)c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int64_t m = m_base + c0 + c;
+                    if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
+                    float v = __uint_as_float(r[c]) * scale;
+                    if (p.KO > 0) {
+                        const A* xrow = xo + m * p.ldxo;  // same address in every lane: broadcast load
+#pragma unroll
+                        for (int j = 0; j < kMaxKO; ++j)
+                            if (j < p.KO) v = fmaf(Widen<A>::to_float(__ldg(xrow + j)), wo_row[j], v);
+                    }
+                    v += bias;
+                    if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+        }
+    } else {
+        // ------------------------------ converters ------------------------------
+        const int cid = (warp - (2 + kEpiWarps)) * 32 + lane;  // 0 .. 255
+        uint32_t iw = 0, ia = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const uint32_t s_w = iw % kStagesW8, ph_w = (iw / kStagesW8) & 1u;
+                const uint32_t s_a = ia % kStagesA, ph_a = (ia / kStagesA) & 1u;
+                ok = mbar_wait(full_w8 + 8 * s_w, ph_w, abort_flag) && mbar_wait(empty_a + 8 * s_a, ph_a ^ 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t src = sw8 + s_w * kBytesW8, dst = sa + s_a * kBytesA;
+#pragma unroll
+                for (int pass = 0; pass < (kTileN * kBlockK / 16) / (kConvWarps * 32); ++pass) {
+                    const int id = pass * (kConvWarps * 32) + cid;  // 16-byte chunk of the int8 tile
+                    const int row = id >> 2, j = id & 3;            // row of 64 codes, chunk j = k 16j .. 16j+15
+                    uint32_t c0, c1, c2, c3;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                                 : "r"(src + (uint32_t)(row * 64 + j * 16)));
+                    uint32_t o[8];
+                    Widen<A>::four(c0, o[0], o[1]);
+                    Widen<A>::four(c1, o[2], o[3]);
+                    Widen<A>::four(c2, o[4], o[5]);
+                    Widen<A>::four(c3, o[6], o[7]);
+                    // 16-bit row = 128 bytes = eight 16-byte chunks; chunk c lives at c ^ (row % 8)
+                    const uint32_t rbase = dst + (uint32_t)(row * 128);
+                    const uint32_t sw = (uint32_t)(row & 7);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rbase + (((uint32_t)(2 * j) ^ sw) << 4)),
+                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                 : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(rbase + (((uint32_t)(2 * j + 1) ^ sw) << 4)),
+                                 "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                                 : "memory");
+                }
+                fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_a + 8 * s_a);
+                    mbar_arrive(empty_w8 + 8 * s_w);
+                }
+                ++iw;
+                ++ia;
+            }
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicExch(p.error_flag, 1u);
+        __nanosleep(200000);  // let any TMA copy still in flight land before the CTA's memory is released
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint64_t inner, uint64_t outer,
+                 uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// One error word per device (file-scope device memory, nothing is allocated), raised by a
+// kernel whose bounded wait expired.
+__device__ unsigned int g_tc_error_word = 0;
+
+unsigned int* error_word() {
+    static unsigned int* words[64] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        void* sym = nullptr;
+        if (cudaGetSymbolAddress(&sym, g_tc_error_word) != cudaSuccess) return nullptr;
+        words[dev] = static_cast<unsigned int*>(sym);
+    }
+    return words[dev];
+}
+
+}  // namespace
+
+bool w8a16_tc_supported(const W8A16Args& a) {
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (a.act_dtype != kBF16 && a.act_dtype != kF16) return false;
+    if (a.K < 16 || a.K % 16 != 0) return false;       // TMA: int8 row stride must be a multiple of 16 bytes
+    if ((a.ldx * 2) % 16 != 0) return false;           // TMA: activation row stride
+    if (!al16(a.x) || !al16(a.wq)) return false;
+    if (a.KO > kMaxKO) return false;
+    if (a.M < 1 || a.N < 1) return false;
+    return encode_fn() != nullptr;
+}
+
+// Activation rows per tile: the multiple of 16 (<= 256) that wastes the fewest SM-slots over the
+// persistent schedule of ceil(M / tile) * ceil(N / 128) tiles on `sms` CTAs.
+static int pick_tile_x(int64_t M, int64_t N, int sms) {
+    const int64_t tiles_n = (N + kTileN - 1) / kTileN;
+    int best = 256;
+    double best_cost = 1e30;
+    for (int tx = 256; tx >= 32; tx -= 16) {
+        const int64_t tiles = ((M + tx - 1) / tx) * tiles_n;
+        const int64_t waves = (tiles + sms - 1) / sms;
+        // time ~ waves * (tile_x + fixed per-tile overhead expressed in rows)
+        const double cost = (double)waves * (tx + 24);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = tx; }
+    }
+    return best;
+}
+
+cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
+    const int sms = sm_count();
+    TcParams p;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.scales = a.scales; p.scales_dtype = a.scales_dtype;
+    p.bias = a.bias; p.bias_dtype = a.bias_dtype;
+    p.xo = a.xo; p.wo = a.wo; p.KO = a.KO; p.ldxo = a.ldxo;
+    p.y = a.y; p.ldy = a.ldy;
+    p.tile_x = pick_tile_x(a.M, a.N, sms);
+    p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
+    p.tiles_n = (int)((a.N + kTileN - 1) / kTileN);
+    p.error_flag = error_word();
+    if (!p.error_flag) return cudaErrorUnknown;
+
+    CUtensorMap map_x, map_w;
+    const CUtensorMapDataType xdt = a.act_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!make_map_2d(&map_x, xdt, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx * 2, kBlockK, (uint32_t)p.tile_x,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorNotSupported;
+    if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK,
+                     kTileN, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorNotSupported;
+
+    const int64_t tiles = (int64_t)p.tiles_x * p.tiles_n;
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    // the opt-in shared-memory size is a per-device function attribute
+    static bool attr_done[64][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int which = a.act_dtype == kBF16 ? 0 : 1;
+    if (dev >= 0 && dev < 64 && !attr_done[dev][which]) {
+        cudaError_t e = which == 0
+            ? cudaFuncSetAttribute(w8a16_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
+            : cudaFuncSetAttribute(w8a16_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev][which] = true;
+    }
+    if (which == 0) w8a16_tc_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, s>>>(map_x, map_w, p);
+    else w8a16_tc_kernel<__half><<<grid, kThreads, kSmemBytes, s>>>(map_x, map_w, p);
+    return cudaPeekAtLastError();
+}
+
+// 0 = no kernel of this library has hit a bounded-wait expiry on the current device
+cudaError_t w8a16_tc_read_error(unsigned int* host_value, cudaStream_t s) {
+    unsigned int* w = error_word();
+    if (!w) return cudaErrorUnknown;
+    cudaError_t e = cudaMemcpyAsync(host_value, w, sizeof(unsigned int), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return e;
+    return cudaStreamSynchronize(s);
+}
+
 }  // namespace cb

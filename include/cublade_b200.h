@@ -134,6 +134,11 @@ int32_t cb_w8a16_linear(const void* x, int64_t M, int64_t K, int64_t ldx, const 
                         const void* xo, int64_t ldxo, const void* wo, int64_t KO, void* y, int64_t ldy,
                         int32_t act_dtype, void* workspace, size_t workspace_bytes, int32_t path, void* stream);
 
+/* Every in-kernel wait of the tensor-core path is bounded; a kernel whose wait expired raises a
+ * per-device flag and returns instead of hanging.  This call synchronises `stream` and copies the
+ * flag (0 = never raised) to *host_flag.  No counterpart in the reference. */
+int32_t cb_device_error_state(uint32_t* host_flag, void* stream);
+
 /* dst[m, j] = src[m, cols[j]]: re-packs activation columns for the outlier split
  * (the two fancy-index gathers of cublade/quantization/linear.py:101-102). elem_size 2 or 4. */
 int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols, void* dst,

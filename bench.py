@@ -254,7 +254,120 @@ class Int8GroupWorkload(Int8ChannelWorkload):
         return O.int8_dequantize_rows(q, s, torch.bfloat16)
 
 
-WORKLOADS = {"int8_channel": Int8ChannelWorkload, "fp8_tensor": Fp8TensorWorkload, "int8_group": Int8GroupWorkload}
+class Fp8ShardedWorkload(Int8ChannelWorkload):
+    """Per-tensor FP8 E4M3 quantize + dequantize of ONE bf16 tensor of 2^33 elements, N(0,1), rows
+    split contiguously over the ranks (strong scaling): local amax, one NCCL max-allreduce of a
+    float32, cast; dequantize is local.  Two HBM passes over x are compulsory (5 B/elem) because a
+    2 GiB..16 GiB shard cannot stay on chip between the amax and the cast."""
+
+    name = "fp8_sharded"
+    dtype = "e4m3"
+    dominant = "cast_tensor_kernel (per-tensor FP8 cast over the local shard)"
+    use_graphs = False
+    scaling = "strong"
+    TOTAL = 1 << 33
+    CHUNK = 1 << 27
+
+    def __init__(self, device, world=1, rank=0, total=None):
+        from cublade_b200 import workloads as W
+        from cublade_b200.sharding import shard_range
+
+        self.total = total or self.TOTAL
+        self.rows, self.cols = self.total // 8192, 8192
+        self.world, self.rank, self.sets = world, rank, 1
+        nchunks = self.total // self.CHUNK
+        c0, c1 = shard_range(nchunks, rank, world)
+        self.n = (c1 - c0) * self.CHUNK
+        self.device = device
+        if device is None:
+            self.x_host = W.sharded_fp8_chunk(0, self.CHUNK, device="cpu")
+            self.x, self.y_host = [], None
+        else:
+            x = torch.empty(self.n, dtype=torch.bfloat16, device=device)
+            for i, c in enumerate(range(c0, c1)):
+                x[i * self.CHUNK:(i + 1) * self.CHUNK] = W.sharded_fp8_chunk(c, self.CHUNK, device=device)
+            self.x = [x.view(-1, 8192)]
+            self.x_host = torch.empty(self.CHUNK, dtype=torch.bfloat16).pin_memory()
+            self.x_host.copy_(x[: self.CHUNK])
+            self.y_host = torch.empty(self.CHUNK, dtype=torch.bfloat16).pin_memory()
+        # algorithmic bytes of the WHOLE tensor per step: quant 5 B/elem, dequant 3 B/elem
+        self.q_bytes_total = self.total * 5
+        self.dq_bytes_total = self.total * 3
+        self.bytes_per_step_total = self.q_bytes_total + self.dq_bytes_total
+        self.q_bytes = self.n * 3  # the cast kernel alone on the local shard (x read + q write)
+        self.dq_bytes = self.n * 3
+        self.bytes_per_step = self.n * 8
+        self.qt = [None]
+        self.launches_per_step = 3
+
+    def config(self):
+        return {"workload": f"fp8_e4m3_per_tensor_sharded_quant+dequant bf16 2^{self.total.bit_length() - 1} elements "
+                            f"N(0,1) over {self.world} GPU(s), NCCL max-allreduce of the fp32 amax",
+                "bytes_per_step": self.bytes_per_step_total,
+                "l2_policy": "inputs larger than L2 (local shard >= 2 GiB)", "seed": 4}
+
+    def quantize(self, x):
+        from cublade_b200.sharding import quantize_tensor_sharded
+
+        return quantize_tensor_sharded(x, dtype=torch.float8_e4m3fn)
+
+    def step_e2e(self, i):
+        # one 2^27-element chunk per step from pinned host memory and back (the full shard would
+        # only time PCIe); the amax exchange still runs
+        x = self.x_host.to(self.device, non_blocking=True)
+        y = self.dequantize(self.quantize(x))
+        self.y_host.copy_(y, non_blocking=True)
+        return y
+
+    e2e_h2d = property(lambda self: self.CHUNK * 2)
+    e2e_d2h = property(lambda self: self.CHUNK * 2)
+    e2e_bytes = property(lambda self: self.CHUNK * 8)
+
+    def cpu_step(self, x_cpu):
+        from oracle import oracle as O
+
+        q, s = O.fp8_quantize(x_cpu)
+        return O.fp8_dequantize(q, s, torch.bfloat16)
+
+
+WORKLOADS = {"int8_channel": Int8ChannelWorkload, "fp8_tensor": Fp8TensorWorkload, "int8_group": Int8GroupWorkload,
+             "fp8_sharded": Fp8ShardedWorkload}
+
+
+def w8a16_extras(device, peaks, ms=(1, 16, 128, 2048)):
+    """W8A16 linear (N=14336, K=4096, per-output-channel int8 weights, bf16 activations) timed per M:
+    TFLOP/s and the roofline that bounds each shape (HBM for the weight stream, tensor for M=2048)."""
+    from cublade_b200 import workloads as W
+    import cublade_b200 as cb
+
+    out = {}
+    w, _, _ = W.w8a16_case(1)
+    layer = cb.cuBladeW8A16LinearLayer(4096, 14336, bias=False, dtype=torch.bfloat16)
+    layer.quantize(w.to(device))
+    layer = layer.to(device)
+    N_, K_ = 14336, 4096
+    for M in ms:
+        # enough distinct activation buffers; the 58.7 MB weight is evicted by an L2-sized scrub between launches
+        x = torch.randn(M, K_, device=device, dtype=torch.float32).to(torch.bfloat16)
+        scrub = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=device)
+        for _ in range(3):
+            layer(x)
+        reps = 20
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        for a, b in evs:
+            scrub.zero_()  # flush L2 so every launch streams the weights from HBM
+            a.record()
+            layer(x)
+            b.record()
+        torch.cuda.synchronize()
+        t = sorted(a.elapsed_time(b) for a, b in evs)[reps // 2] * 1e-3
+        flops = 2.0 * M * N_ * K_
+        bytes_ = N_ * K_ + 2 * N_ + 2 * M * K_ + 2 * M * N_
+        tf, gbs = flops / t / 1e12, bytes_ / t / 1e9
+        bound = "tensor" if M >= 1024 else "hbm"
+        frac = tf / peaks["bf16_tflops"] if bound == "tensor" else gbs / peaks["hbm_gbs"]
+        out[f"M={M}"] = {"us": t * 1e6, "tflops": tf, "gbs": gbs, "bound": bound, "frac": frac}
+    return out
 
 
 # --------------------------------------------------------------------------------------
@@ -263,6 +376,8 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     wl = WORKLOADS[args.workload](None)
+    if args.workload == "fp8_sharded":  # bounded sample: one 2^27-element chunk, scaled to the metric's unit
+        wl.bytes_per_step = wl.CHUNK * 8
     x = wl.cpu_input()
     cores = torch.get_num_threads()
     for _ in range(max(1, min(args.warmup, 2))):
@@ -296,8 +411,12 @@ def cpu_baseline(wl, budget_s=12.0):
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
         reps += 1
-    return {"value": wl.bytes_per_step / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"full {wl.rows}x{wl.cols} tensor, best of {reps} (PyTorch CPU formulation of the reference ops)"}
+    nbytes = x.numel() * (8 if getattr(wl, "scaling", "weak") == "strong" else 6) + 0
+    if getattr(wl, "scaling", "weak") != "strong":
+        nbytes = wl.bytes_per_step
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"tensor of {tuple(x.shape)} ({x.numel()} elements), best of {reps} "
+                      "(PyTorch CPU formulation of the reference ops)"}
 
 
 def main():
@@ -308,6 +427,7 @@ def main():
     ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="cublade_b200", choices=["cublade_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-w8a16", action="store_true", help="skip the W8A16 TFLOP/s table")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -332,8 +452,12 @@ def main():
 
     N.lib()  # fail loudly if the extension is missing
     warmup = max(args.warmup, 3)
-    wl = WORKLOADS[args.workload](device)
+    if args.workload == "fp8_sharded":
+        wl = Fp8ShardedWorkload(device, world=world, rank=rank)
+    else:
+        wl = WORKLOADS[args.workload](device)
     wl.prime()
+    use_graphs = getattr(wl, "use_graphs", True)
 
     def barrier():
         if dist is not None:
@@ -350,16 +474,33 @@ def main():
     side = torch.cuda.Stream()
     step_graphs, q_graphs, dq_graphs, keep = [], [], [], []
     static_qt = list(wl.qt)
-    with torch.cuda.stream(side):
-        for i in range(wl.sets):
-            for kind, bucket in (("step", step_graphs), ("q", q_graphs), ("dq", dq_graphs)):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    if kind in ("step", "q"):
-                        keep.append(wl.quantize(wl.x[i]))
-                    if kind in ("step", "dq"):
-                        keep.append(wl.dequantize(static_qt[(i + 1) % wl.sets]))
-                bucket.append(g)
+
+    class Eager:  # same interface as a CUDA graph, launches through the Python API every time
+        def __init__(self, fn):
+            self.fn = fn
+
+        def replay(self):
+            self.fn()
+
+    if use_graphs:
+        with torch.cuda.stream(side):
+            for i in range(wl.sets):
+                for kind, bucket in (("step", step_graphs), ("q", q_graphs), ("dq", dq_graphs)):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        if kind in ("step", "q"):
+                            keep.append(wl.quantize(wl.x[i]))
+                        if kind in ("step", "dq"):
+                            keep.append(wl.dequantize(static_qt[(i + 1) % wl.sets]))
+                    bucket.append(g)
+    else:
+        from cublade_b200.bindings.cuda.split_phase import amax_abs, cast_per_tensor
+
+        step_graphs = [Eager(lambda: wl.step(0))]
+        # the dominant kernel alone: the cast over the local shard with a precomputed global amax
+        amax_static = amax_abs(wl.x[0])
+        q_graphs = [Eager(lambda: cast_per_tensor(wl.x[0], amax_static, torch.float8_e4m3fn))]
+        dq_graphs = [Eager(lambda: wl.dequantize(static_qt[0]))]
     torch.cuda.synchronize()
 
     def timed(graphs, n):
@@ -386,7 +527,9 @@ def main():
         t = torch.tensor([ms_per_step], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_per_step = float(t.item())
-    value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    strong = getattr(wl, "scaling", "weak") == "strong"
+    step_bytes = wl.bytes_per_step_total if strong else world * wl.bytes_per_step
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
 
     # eager (no graph) pacing of the same step through the Python API, for information
     barrier()
@@ -414,15 +557,17 @@ def main():
         t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_value = world * wl.bytes_per_step / (e2e_ms * 1e-3) / 1e9
+    e2e_value = world * getattr(wl, "e2e_bytes", wl.bytes_per_step) / (e2e_ms * 1e-3) / 1e9
 
     if rank == 0:
         peaks = _peaks()
         achieved = wl.q_bytes / (q_avg * 1e-3) / 1e9
         out = {
             "metric": "quant/dequant GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": K,
-            "warmup": warmup, "ms_per_step": ms_per_step, "eager_ms_per_step": eager_ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": dict(wl.config(), launch="one CUDA graph per step (quantize + dequantize nodes)"),
+            "warmup": warmup, "ms_per_step": ms_per_step, "eager_ms_per_step": eager_ms, "higher_is_better": True, "scaling": "strong" if strong else "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": dict(wl.config(), launch="one CUDA graph per step (quantize + dequantize nodes)" if use_graphs
+                           else "eager launches through the Python API"),
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": wl.e2e_h2d, "d2h_bytes_per_step": wl.e2e_d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
@@ -435,6 +580,8 @@ def main():
                         "dequantize": {"avg_us": dq_avg * 1e3, "gbs": wl.dq_bytes / (dq_avg * 1e-3) / 1e9,
                                        "frac": wl.dq_bytes / (dq_avg * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
         }
+        if not args.no_w8a16:
+            out["w8a16"] = w8a16_extras(device, peaks)
         if not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(out))

@@ -1,0 +1,124 @@
+"""Single-node multi-GPU use of the quantization path: one process per GPU, ``torch.distributed``.
+
+The reference has no multi-GPU code; this module adds only what the path needs.
+
+* Per-channel / per-group quantization and every dequantization shard by rows with NO
+  communication: each rank calls the ordinary single-GPU functions on its rows.
+* Per-tensor quantization (FP8 or INT8) needs the global amax: each rank reduces its shard
+  (``amax_abs``), the ranks max-allreduce ONE float32 (exact and order independent, so the sharded
+  result is bit-identical to the single-GPU result), then each rank casts its shard.
+* The W8A16 linear shards its output features: per-output-channel scales make the row blocks of
+  ``int8_weights`` independent; activations are replicated.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .quantization.tensor import QuantizedTensor
+
+
+def shard_range(n: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Contiguous, balanced split of ``n`` rows: the first ``n % world_size`` ranks get one extra row."""
+    if not (0 <= rank < world_size):
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    base, extra = divmod(n, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def _native_ops():
+    from .bindings.cuda.split_phase import amax_abs, cast_per_tensor
+
+    return SimpleNamespace(amax_abs=amax_abs, cast_per_tensor=cast_per_tensor)
+
+
+def quantize_tensor_sharded(x_local: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn, eps: float = 1e-12,
+                            group=None, ops=None) -> QuantizedTensor:
+    """Per-tensor quantization of a tensor whose rows are spread over the ranks of ``group``.
+
+    Every rank passes its own contiguous shard and receives the codes of that shard plus the
+    (identical on all ranks) global scale.  One collective: ``all_reduce(MAX)`` of a float32 scalar.
+    ``ops`` replaces the two kernels (used by CPU tests of the orchestration).
+    """
+    import torch.distributed as dist
+
+    ops = ops or _native_ops()
+    amax = ops.amax_abs(x_local)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    q, scale = ops.cast_per_tensor(x_local, amax, dtype, eps)
+    zp = torch.zeros((), dtype=torch.float32, device=x_local.device)
+    return QuantizedTensor(q, scale, zp, "tensor", 0, 32, dtype, x_local.dtype)
+
+
+def shard_w8a16_layer(layer, rank: int, world_size: int):
+    """Keep only this rank's block of output features of a quantized ``cuBladeW8A16LinearLayer`` (in place).
+
+    ``int8_weights``, ``scales``, ``bias`` and ``outlier_weights`` are sliced along dim 0; the column
+    index buffers are unchanged.  The layer then maps ``[..., in] -> [..., out / world_size]``.
+    """
+    start, stop = shard_range(layer.out_features, rank, world_size)
+    layer.int8_weights = layer.int8_weights[start:stop].contiguous()
+    layer.scales = layer.scales[start:stop].contiguous()
+    if layer.outlier_weights is not None:
+        layer.outlier_weights = layer.outlier_weights[start:stop].contiguous()
+    if layer.bias is not None:
+        layer.bias = nn.Parameter(layer.bias.detach()[start:stop].contiguous(), requires_grad=layer.bias.requires_grad)
+    layer.out_features = stop - start
+    layer.shard = (rank, world_size, start, stop)
+    layer._dev_cache = {}
+    return layer
+
+
+def quantize_model_sharded(model: nn.Module, rank: int, world_size: int, quant_type: str = "w8a16",
+                           target_modules: Optional[List[str]] = None, exclude_modules: Optional[List[str]] = None,
+                           **quant_kwargs) -> nn.Module:
+    """``quantize_model`` where each rank quantizes and keeps only its ``out_features / world_size`` rows
+    of every selected ``nn.Linear`` (no communication: per-channel scales are row-local).
+
+    Selection rules are those of ``quantize_model``.  The resulting layers are column-parallel: their
+    outputs are this rank's slice of the full output.
+    """
+    from .quantization.quantizers import QUANT_LAYER_REGISTRY, _init_registry
+
+    _init_registry()
+    if quant_type not in QUANT_LAYER_REGISTRY:
+        raise ValueError(f"Unknown quant_type '{quant_type}'. Available: {', '.join(QUANT_LAYER_REGISTRY)}")
+    layer_cls = QUANT_LAYER_REGISTRY[quant_type]
+    exclude_modules = exclude_modules or []
+
+    def walk(module: nn.Module, prefix: str):
+        for name, child in list(module.named_children()):
+            path = f"{prefix}.{name}" if prefix else name
+            if not isinstance(child, nn.Linear):
+                walk(child, path)
+                continue
+            if any(pat in path for pat in exclude_modules):
+                continue
+            if target_modules is not None and not any(pat in path for pat in target_modules):
+                continue
+            start, stop = shard_range(child.out_features, rank, world_size)
+            new = layer_cls(child.in_features, stop - start, bias=child.bias is not None, dtype=child.weight.dtype,
+                            **quant_kwargs)
+            setattr(module, name, new)
+            new.quantize(child.weight.detach()[start:stop])
+            if child.bias is not None:
+                new.bias = nn.Parameter(child.bias.detach()[start:stop].clone(), requires_grad=False)
+            new.shard = (rank, world_size, start, stop)
+
+    walk(model, "")
+    return model
+
+
+def all_gather_columns(y_local: torch.Tensor, group=None) -> torch.Tensor:
+    """Concatenate the ranks' output-feature slices along the last dim (equal slice widths)."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    parts = [torch.empty_like(y_local) for _ in range(world)]
+    dist.all_gather(parts, y_local.contiguous(), group=group)
+    return torch.cat(parts, dim=-1)

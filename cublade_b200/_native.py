@@ -45,6 +45,11 @@ SIGNATURES = {
                                    c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p,
                                    c_size_t, c_int32, c_void_p]),
     "cb_device_error_state": (c_int32, [c_void_p, c_void_p]),
+    "cb_static_scratch_bytes": (c_size_t, []),
+    "cb_static_last_error": (c_char_p, []),
+    "cb_w8a16_linear_outlier_static": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64,
+                                                  c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int32, c_void_p,
+                                                  c_void_p, c_int64, c_int32, c_void_p]),
     "cb_gather_columns": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p]),
 }
 

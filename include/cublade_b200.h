@@ -144,6 +144,30 @@ int32_t cb_device_error_state(uint32_t* host_flag, void* stream);
 int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols, void* dst,
                           int64_t ld_dst, int32_t elem_size, void* stream);
 
+/* ------------------------------------------------------------------------
+ * LLM.int8 W8A16 linear for callers that cannot allocate device memory.
+ * No counterpart in the reference (which allocates freely through torch).
+ *
+ * Same result as: cb_gather_columns(x, normal_cols) ; cb_gather_columns(x, outlier_cols) ;
+ * cb_w8a16_linear(...), but the two re-packed activation buffers live in a 16 MiB array that is
+ * part of the library's device image (every GPU that loads the library holds it until exit), so
+ * the call needs nothing but its inputs and its output and makes no cudaMalloc / cudaFree.
+ *   x [M, K] activations (act_dtype, row stride ldx);  normal_cols int64[K - KO] and
+ *   outlier_cols int64[KO] are DEVICE arrays of column indices;  wq int8 [N, K - KO];
+ *   wo [N, KO] in act_dtype;  y [M, N].
+ * Limit: M * (round_up(K - KO, 8) + round_up(KO, 8)) * 2 bytes <= cb_static_scratch_bytes(),
+ *   otherwise CB_ERR_RANGE with an explanatory cb_static_last_error(); nothing is launched.
+ * The first call on a device resolves the array's address; issue it before any stream capture.
+ * All calls on a device share the array: it keeps the last call's contents (each call writes
+ * what it reads, nothing must be pre-zeroed) and calls that overlap on the GPU race on it.
+ * ------------------------------------------------------------------------ */
+size_t cb_static_scratch_bytes(void);
+const char* cb_static_last_error(void);
+int32_t cb_w8a16_linear_outlier_static(const void* x, int64_t M, int64_t K, int64_t ldx, const int64_t* normal_cols,
+                                       const int64_t* outlier_cols, int64_t KO, const void* wq, int64_t N,
+                                       const void* scales, int32_t scales_dtype, const void* bias, int32_t bias_dtype,
+                                       const void* wo, void* y, int64_t ldy, int32_t act_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

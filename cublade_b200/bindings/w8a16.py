@@ -12,7 +12,7 @@ import torch
 
 from .. import _native as N
 
-PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE = 0, 1, 2
+PATH_AUTO, PATH_STREAM, PATH_TENSOR_CORE, PATH_TENSOR_CORE_SINGLE = 0, 1, 2, 3
 
 
 def _check_2d(t: torch.Tensor, name: str) -> None:
@@ -54,7 +54,7 @@ def w8a16_linear(
         scales: ``[N]`` float16 / bfloat16 / float32.
         bias: optional ``[N]``.
         x_outlier, w_outlier: optional ``[M, KO]`` / ``[N, KO]`` in ``x2d.dtype`` (LLM.int8 side product).
-        path: 0 automatic, 1 weight-streaming kernel, 2 tcgen05 kernel.
+        path: 0 automatic, 1 weight-streaming kernel, 2 tcgen05 CTA-pair kernel, 3 tcgen05 single-CTA kernel.
     """
     if not x2d.is_cuda:
         raise ValueError(f"w8a16_linear: activations must be on CUDA, got device={x2d.device}")

@@ -55,6 +55,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         obj = OBJ / (src.stem + ".o")
         if force or _stale(obj, [src, *headers]):
             flags = [f for f in NVCC_FLAGS if not (src.name in FMAD_OK and f == "-fmad=false")]
+            flags += os.environ.get("CB_EXTRA_NVCC_FLAGS", "").split()
             cmd = [nvcc, *flags, "-Xptxas", "-v" if verbose else "-O3", "-c", str(src), "-o", str(obj)]
             jobs.append((src, cmd))
 

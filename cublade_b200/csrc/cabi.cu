@@ -165,7 +165,7 @@ int32_t cb_w8a16_linear(const void* x, int64_t M, int64_t K, int64_t ldx, const 
     if (!x || !wq || !scales || !y) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: null pointer");
     if (KO > 0 && (!xo || !wo)) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: KO > 0 needs xo and wo");
     if (ldx < K || ldy < N || (KO > 0 && ldxo < KO)) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: row stride too small");
-    if (path < 0 || path > 2) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: path must be 0, 1 or 2");
+    if (path < 0 || path > 3) return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear: path must be 0, 1, 2 or 3");
     const size_t need = cb::w8a16_workspace_bytes(M, N, K);
     if (need > 0 && (!workspace || workspace_bytes < need))
         return fail(CB_ERR_WORKSPACE, "cb_w8a16_linear: workspace of %zu bytes required", need);

@@ -54,7 +54,7 @@ struct W8A16Args {
     size_t workspace_bytes;
 };
 size_t w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
-// path: 0 = automatic, 1 = weight-streaming (skinny M) kernel, 2 = tcgen05 GEMM
+// path: 0 = automatic, 1 = weight-streaming (skinny M) kernel, 2 = tcgen05 CTA-pair GEMM, 3 = tcgen05 single-CTA GEMM
 cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s);
 // reads (and leaves untouched) the per-device flag a kernel raises when one of its bounded waits
 // expired; synchronises the stream.

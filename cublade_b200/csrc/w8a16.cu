@@ -1,5 +1,6 @@
-// W8A16 dispatch: picks the weight-streaming kernel (w8a16_stream.cu) for skinny
-// activations and the tcgen05 tensor-core kernel (w8a16_tc.cu) for tall ones.
+// W8A16 dispatch: the weight-streaming kernel (w8a16_stream.cu) for skinny activations, the
+// tcgen05 CTA-pair kernel (w8a16_tc2.cu) for tall ones, the single-CTA tcgen05 kernel
+// (w8a16_tc.cu) when a pair cannot be used.
 #include "launch.h"
 
 namespace cb {
@@ -7,16 +8,22 @@ namespace cb {
 cudaError_t launch_w8a16_stream(const W8A16Args& a, cudaStream_t s);
 cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s);
 bool w8a16_tc_supported(const W8A16Args& a);
+cudaError_t launch_w8a16_tc_pair(const W8A16Args& a, cudaStream_t s);
+bool w8a16_tc_pair_supported(const W8A16Args& a);
 
-// Rows of activations from which the tensor-core kernel is used when the shape allows it.
+// Rows of activations from which the tensor-core kernels are used when the shape allows it.
 constexpr int64_t kTcMinM = 65;
 
 size_t w8a16_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
 
 cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s) {
     if (path == 1) return launch_w8a16_stream(a, s);
-    if (path == 2) return w8a16_tc_supported(a) ? launch_w8a16_tc(a, s) : cudaErrorNotSupported;
-    if (a.M >= kTcMinM && w8a16_tc_supported(a)) return launch_w8a16_tc(a, s);
+    if (path == 2) return w8a16_tc_pair_supported(a) ? launch_w8a16_tc_pair(a, s) : cudaErrorNotSupported;
+    if (path == 3) return w8a16_tc_supported(a) ? launch_w8a16_tc(a, s) : cudaErrorNotSupported;
+    if (a.M >= kTcMinM) {
+        if (w8a16_tc_pair_supported(a)) return launch_w8a16_tc_pair(a, s);
+        if (w8a16_tc_supported(a)) return launch_w8a16_tc(a, s);
+    }
     return launch_w8a16_stream(a, s);
 }
 

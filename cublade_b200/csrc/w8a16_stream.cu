@@ -185,35 +185,74 @@ __global__ void __launch_bounds__(kWarps * 32) w8a16_stream_kernel(const StreamP
     const int8_t* w1 = p.wq + (n0 + g + 8) * p.K;
     const int kper = VEC >= 4 ? VEC : 4;
 
-    // this warp's K slice: rounds of KSTEP, interleaved over the four warps in
-    // groups of 4 rounds so each warp streams contiguous 4*KSTEP-byte runs.
+    // This warp's K slice: rounds of KSTEP, dealt to the four warps in groups of U rounds.  The
+    // loop is software-pipelined over two register stages: the loads of the next group (weights,
+    // and the activations too when they fit in registers) are issued before the current group is
+    // widened and multiplied, so HBM latency overlaps the arithmetic inside each warp.
+    constexpr int U = 2;
+    constexpr int CW = VEC >= 4 ? VEC / 4 : 1;
+    constexpr int XW = VEC >= 4 ? VEC / 2 : 2;
+    constexpr bool kPrefetchX = MT <= 2;
+    struct Stage {
+        uint32_t c0[U][CW], c1[U][CW];
+        uint32_t xa[kPrefetchX ? U : 1][kPrefetchX ? MT : 1][XW];
+    };
     const int64_t nrounds = (p.K + KSTEP - 1) / KSTEP;
-    for (int64_t r = (int64_t)warp * 4; r < nrounds; r += kWarps * 4) {
-        uint32_t c0[4][VEC >= 4 ? VEC / 4 : 1], c1[4][VEC >= 4 ? VEC / 4 : 1];
+    auto load_stage = [&](Stage& st, int64_t r) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
+            const bool valid = (r + u) < nrounds;
             const int64_t k = (r + u) * KSTEP + (int64_t)t * kper;
-            load_codes<VEC>(w0, k, p.K, r0_ok && (r + u) < nrounds, c0[u]);
-            load_codes<VEC>(w1, k, p.K, r1_ok && (r + u) < nrounds, c1[u]);
+            load_codes<VEC>(w0, k, p.K, r0_ok && valid, st.c0[u]);
+            load_codes<VEC>(w1, k, p.K, r1_ok && valid, st.c1[u]);
+            if constexpr (kPrefetchX) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int64_t m = p.m0 + mt * 8 + g;
+                    load_acts<A, VEC>(x + m * p.ldx, k, p.K, valid && m < p.M, st.xa[u][mt]);
+                }
+            }
         }
+    };
+    auto compute_stage = [&](Stage& st, int64_t r) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int64_t k = (r + u) * KSTEP + (int64_t)t * kper;
+        for (int u = 0; u < U; ++u) {
             if ((r + u) >= nrounds) continue;
-            uint32_t xa[MT][VEC >= 4 ? VEC / 2 : 2];
+            uint32_t xl[kPrefetchX ? 1 : MT][XW];
+            if constexpr (!kPrefetchX) {
+                const int64_t k = (r + u) * KSTEP + (int64_t)t * kper;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const int64_t m = p.m0 + mt * 8 + g;
-                load_acts<A, VEC>(x + m * p.ldx, k, p.K, m < p.M, xa[mt]);
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int64_t m = p.m0 + mt * 8 + g;
+                    load_acts<A, VEC>(x + m * p.ldx, k, p.K, m < p.M, xl[mt]);
+                }
             }
 #pragma unroll
             for (int s = 0; s < NSTEP; ++s) {
                 uint32_t a[4];
-                Act<A>::widen4(c0[u][s], a[0], a[2]);
-                Act<A>::widen4(c1[u][s], a[1], a[3]);
+                Act<A>::widen4(st.c0[u][s], a[0], a[2]);
+                Act<A>::widen4(st.c1[u][s], a[1], a[3]);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) Act<A>::mma(acc[mt], a, xa[mt][2 * s], xa[mt][2 * s + 1]);
+                for (int mt = 0; mt < MT; ++mt) {
+                    if constexpr (kPrefetchX) Act<A>::mma(acc[mt], a, st.xa[u][mt][2 * s], st.xa[u][mt][2 * s + 1]);
+                    else Act<A>::mma(acc[mt], a, xl[mt][2 * s], xl[mt][2 * s + 1]);
+                }
             }
+        }
+    };
+    {
+        Stage st0, st1;
+        int64_t r = (int64_t)warp * U;
+        const int64_t step = (int64_t)kWarps * U;
+        load_stage(st0, r);
+        while (r < nrounds) {
+            load_stage(st1, r + step);
+            compute_stage(st0, r);
+            r += step;
+            if (r >= nrounds) break;
+            load_stage(st0, r + step);
+            compute_stage(st1, r);
+            r += step;
         }
     }
 

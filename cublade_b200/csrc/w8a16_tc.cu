@@ -28,11 +28,7 @@
 // kernel raises an error flag in global memory, every role leaves its loop, TMEM is released and
 // the kernel returns.
 
-#include "launch.h"
-
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
+#include "tc_common.cuh"
 
 #include <cstdio>
 #include <mutex>
@@ -41,8 +37,9 @@ namespace cb {
 
 namespace {
 
+using namespace tc;
+
 constexpr int kTileN = 128;     // weight rows (output features) per tile = UMMA M
-constexpr int kBlockK = 64;     // k per pipeline stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int kMaxTileX = 256;  // activation rows per tile = UMMA N (multiple of 16)
 constexpr int kStagesX = 4;     // activation tiles in flight (32 KiB each at 256 rows)
 constexpr int kStagesA = 3;     // converted weight tiles (16 KiB each)
@@ -68,158 +65,6 @@ struct SmemLayout {
     static constexpr uint32_t total = abort_flag + 4;
 };
 constexpr uint32_t kSmemBytes = SmemLayout::total + 1024;  // + slack to align the base to 1024 B
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait (about one second of SM clocks).  Returns false on expiry or when another role
-// has already raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > 2000000000LL) {
-            *abort_flag = 1u;
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes (64 16-bit
-// elements) in the 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), descriptor
-// version 1, layout type 2 (SWIZZLE_128B).  Advancing k by 16 elements adds 32 bytes to the
-// start address.
-__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);   // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024u >> 4) << 32;               // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                          // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor, kind::f16: fp32 accumulate, A and B of the same 16-bit format, both
-// K-major, M = 128, N = tile_x.
-__device__ __forceinline__ uint32_t make_idesc(bool bf16, uint32_t n) {
-    const uint32_t fmt = bf16 ? 1u : 0u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
-}
-
-template <typename A>
-struct Widen;
-template <>
-struct Widen<__nv_bfloat16> {
-    static constexpr bool kBf16 = true;
-    // four int8 codes -> (c0,c1), (c2,c3) as bf16 pairs; exact (see w8a16_stream.cu)
-    __device__ __forceinline__ static void four(uint32_t c, uint32_t& lo, uint32_t& hi) {
-        const uint32_t u = c ^ 0x80808080u;
-        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
-        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
-        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
-        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
-        lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
-        hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
-    }
-    __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
-    __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
-};
-template <>
-struct Widen<__half> {
-    static constexpr bool kBf16 = false;
-    __device__ __forceinline__ static void four(uint32_t c, uint32_t& lo, uint32_t& hi) {
-        const uint32_t u = c ^ 0x80808080u;
-        const uint32_t p0 = __byte_perm(u, 0x64006400u, 0x7150);
-        const uint32_t p1 = __byte_perm(u, 0x64006400u, 0x7352);
-        const __half2 k = __half2half2(__ushort_as_half((unsigned short)0x6480));
-        __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&p0), k);
-        __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&p1), k);
-        lo = *reinterpret_cast<uint32_t*>(&a);
-        hi = *reinterpret_cast<uint32_t*>(&b);
-    }
-    __device__ __forceinline__ static float to_float(__half v) { return __half2float(v); }
-    __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
-};
-
-__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
-    if (dtype == kF32) return static_cast<const float*>(p)[i];
-    if (dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
-    return __half2float(static_cast<const __half*>(p)[i]);
-}
 
 struct TcParams {
     int64_t M, N, K;
@@ -502,6 +347,8 @@ unsigned int* error_word() {
 
 }  // namespace
 
+unsigned int* w8a16_tc_error_word() { return error_word(); }
+
 bool w8a16_tc_supported(const W8A16Args& a) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (a.act_dtype != kBF16 && a.act_dtype != kF16) return false;
@@ -523,7 +370,7 @@ static int pick_tile_x(int64_t M, int64_t N, int sms) {
         const int64_t tiles = ((M + tx - 1) / tx) * tiles_n;
         const int64_t waves = (tiles + sms - 1) / sms;
         // time ~ waves * (tile_x + fixed per-tile overhead expressed in rows)
-        const double cost = (double)waves * (tx + 24);
+        const double cost = (double)waves * (tx + 512);  // measured: a k-block costs nearly the same for every tile height
         if (cost < best_cost - 1e-9) { best_cost = cost; best = tx; }
     }
     return best;

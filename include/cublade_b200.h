@@ -126,7 +126,7 @@ int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float*
  * bias [N] of bias_dtype or NULL.  xo [M, KO] / wo [N, KO] (act_dtype, KO may
  * be 0 with NULL pointers) carry the LLM.int8 outlier columns kept in 16-bit.
  * fp32 accumulation, one rounding to act_dtype at the end.
- * path: 0 auto, 1 weight-streaming kernel, 2 tcgen05 tensor-core kernel.
+ * path: 0 auto, 1 weight-streaming kernel, 2 tcgen05 CTA-pair kernel, 3 tcgen05 single-CTA kernel.
  * ------------------------------------------------------------------------ */
 size_t cb_w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int32_t cb_w8a16_linear(const void* x, int64_t M, int64_t K, int64_t ldx, const void* wq, int64_t N,

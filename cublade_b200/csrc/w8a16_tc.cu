@@ -14,8 +14,9 @@
 // scalar per TMEM lane, i.e. per epilogue thread; (3) for a fixed column m the 32 lanes of an
 // epilogue warp store 32 consecutive n of y[m, :], a 64-byte contiguous segment.
 //
-// Warp roles in a CTA of 14 warps (one CTA per SM, persistent over output tiles):
-//   warp 0      TMA producer: x tile (bf16/f16, 128-byte swizzle) and int8 weight tile, per k-block
+// Warp roles in a CTA of 15 warps (one CTA per SM, persistent over output tiles):
+//   warp 0      TMA producer: activation tile (bf16/f16, 128-byte swizzle) per k-block
+//   warp 14     TMA producer: int8 weight tile per k-block, plus an L2 prefetch 12 k-blocks ahead
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128, N=tile_x, K=16) x4 per
 //               k-block and commits to the "slot free" / "accumulator ready" barriers; also owns
 //               the TMEM allocation (512 columns = two accumulators)
@@ -46,7 +47,8 @@ constexpr int kStagesA = 3;     // converted weight tiles (16 KiB each)
 constexpr int kStagesW8 = 4;    // int8 weight tiles (8 KiB each)
 constexpr int kConvWarps = 8;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (2 + kEpiWarps + kConvWarps) * 32;
+constexpr int kThreads = (3 + kEpiWarps + kConvWarps) * 32;  // + TMA(x), MMA, TMA(w8)
+constexpr int kW8Warp = 2 + kEpiWarps + kConvWarps;         // last warp: int8 weight producer
 constexpr int kTmemCols = 512;
 
 constexpr uint32_t kBytesX = kMaxTileX * kBlockK * 2;  // 32768
@@ -124,29 +126,42 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ TMA producer, activations ------------------------------
+        // The two producers are separate warps: probing a barrier costs ~130 cycles even when its
+        // phase is complete and issuing a TMA ~100, so one thread feeding both rings cannot stay
+        // ahead of the tensor core.
         if (lane == 0) {
-            uint32_t ix = 0, iw = 0;  // running k-block counters for the two rings
+            uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int tx = t % p.tiles_x, tn = t / p.tiles_x;
-                for (int kb = 0; kb < num_kb && ok; ++kb) {
-                    {
-                        const uint32_t s = iw % kStagesW8, ph = (iw / kStagesW8) & 1u;
-                        ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag);
-                        if (!ok) break;
-                        mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
-                        tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, tn * kTileN, full_w8 + 8 * s);
-                        ++iw;
-                    }
-                    {
-                        const uint32_t s = ix % kStagesX, ph = (ix / kStagesX) & 1u;
-                        ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
-                        if (!ok) break;
-                        mbar_expect_tx(full_x + 8 * s, x_bytes);
-                        tma_load_2d(sx + s * kBytesX, &map_x, kb * kBlockK, tx * p.tile_x, full_x + 8 * s);
-                        ++ix;
-                    }
+                const int row_x = (t % p.tiles_x) * p.tile_x;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(full_x + 8 * s, x_bytes);
+                    tma_load_2d(sx + s * kBytesX, &map_x, kb * kBlockK, row_x, full_x + 8 * s);
+                    if (++s == kStagesX) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == kW8Warp) {
+        // ------------------------------ TMA producer, int8 weights ------------------------------
+        if (lane == 0) {
+            constexpr int kAhead = 12;  // k-blocks of weights requested into L2 ahead of their TMA load
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int row_w = (t / p.tiles_x) * kTileN;
+                const int row_w_next = ((t + (int)gridDim.x) / p.tiles_x) * kTileN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (kb + kAhead < num_kb) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kBlockK, row_w);
+                    else if (t + (int)gridDim.x < total_tiles)
+                        tma_prefetch_l2_2d(&map_w, (kb + kAhead - num_kb) * kBlockK, row_w_next);
+                    ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
+                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, row_w, full_w8 + 8 * s);
+                    if (++s == kStagesW8) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -154,8 +169,11 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             const uint32_t idesc = make_idesc(Widen<A>::kBf16, (uint32_t)p.tile_x);
-            uint32_t ix = 0, ia = 0, it = 0;
-            bool ok = true;
+            // Ring positions are kept incrementally (no divisions) and the barriers of the NEXT
+            // k-block are probed before the MMAs of the current one are issued, so a probe's
+            // latency overlaps the issue; this thread's loop is the critical path of the kernel.
+            uint32_t s_a = 0, ph_a = 0, s_x = 0, ph_x = 0, it = 0;
+            bool ok = true, pre = false;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
                 ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
@@ -163,11 +181,17 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    const uint32_t s_a = ia % kStagesA, ph_a = (ia / kStagesA) & 1u;
-                    const uint32_t s_x = ix % kStagesX, ph_x = (ix / kStagesX) & 1u;
-                    ok = mbar_wait(full_a + 8 * s_a, ph_a, abort_flag) && mbar_wait(full_x + 8 * s_x, ph_x, abort_flag);
-                    if (!ok) break;
+                    if (!pre) {
+                        const bool r0 = mbar_try(full_a + 8 * s_a, ph_a), r1 = mbar_try(full_x + 8 * s_x, ph_x);
+                        ok = (r0 || mbar_wait(full_a + 8 * s_a, ph_a, abort_flag)) &&
+                             (r1 || mbar_wait(full_x + 8 * s_x, ph_x, abort_flag));
+                        if (!ok) break;
+                    }
                     tc_fence_after();
+                    uint32_t ns_a = s_a + 1, nph_a = ph_a, ns_x = s_x + 1, nph_x = ph_x;
+                    if (ns_a == kStagesA) { ns_a = 0; nph_a ^= 1u; }
+                    if (ns_x == kStagesX) { ns_x = 0; nph_x ^= 1u; }
+                    const bool n0 = mbar_try(full_a + 8 * ns_a, nph_a), n1 = mbar_try(full_x + 8 * ns_x, nph_x);
                     const uint64_t adesc = make_kmajor_sw128_desc(sa + s_a * kBytesA);
                     const uint64_t bdesc = make_kmajor_sw128_desc(sx + s_x * kBytesX);
 #pragma unroll
@@ -178,8 +202,8 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                     umma_commit(empty_a + 8 * s_a);  // both operand slots are free once these MMAs retire
                     umma_commit(empty_x + 8 * s_x);
-                    ++ia;
-                    ++ix;
+                    pre = n0 && n1;
+                    s_a = ns_a; ph_a = nph_a; s_x = ns_x; ph_x = nph_x;
                 }
                 if (!ok) break;
                 umma_commit(tmem_full + 8 * acc);  // accumulator complete -> epilogue
@@ -206,7 +230,11 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 for (int j = 0; j < kMaxKO; ++j)
                     wo_row[j] = (n_ok && j < p.KO) ? Widen<A>::to_float(wo[n * p.KO + j]) : 0.0f;
             }
-            ok = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag);
+            {
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+            }
             if (!ok) break;
             tc_fence_after();
             const int64_t m_base = (int64_t)tx * p.tile_x;
@@ -233,16 +261,23 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
         }
-    } else {
+    } else if (warp < kW8Warp) {
         // ------------------------------ converters ------------------------------
         const int cid = (warp - (2 + kEpiWarps)) * 32 + lane;  // 0 .. 255
-        uint32_t iw = 0, ia = 0;
+        uint32_t s_w = 0, ph_w = 0, s_a = 0, ph_a = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             for (int kb = 0; kb < num_kb; ++kb) {
-                const uint32_t s_w = iw % kStagesW8, ph_w = (iw / kStagesW8) & 1u;
-                const uint32_t s_a = ia % kStagesA, ph_a = (ia / kStagesA) & 1u;
-                ok = mbar_wait(full_w8 + 8 * s_w, ph_w, abort_flag) && mbar_wait(empty_a + 8 * s_a, ph_a ^ 1u, abort_flag);
+                {
+                    // lane 0 probes both barriers back to back, the warp shares the verdict
+                    int okw = 1;
+                    if (lane == 0) {
+                        const bool r0 = mbar_try(full_w8 + 8 * s_w, ph_w), r1 = mbar_try(empty_a + 8 * s_a, ph_a ^ 1u);
+                        okw = ((r0 || mbar_wait(full_w8 + 8 * s_w, ph_w, abort_flag)) &&
+                               (r1 || mbar_wait(empty_a + 8 * s_a, ph_a ^ 1u, abort_flag))) ? 1 : 0;
+                    }
+                    ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t src = sw8 + s_w * kBytesW8, dst = sa + s_a * kBytesA;
@@ -276,8 +311,8 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     mbar_arrive(full_a + 8 * s_a);
                     mbar_arrive(empty_w8 + 8 * s_w);
                 }
-                ++iw;
-                ++ia;
+                if (++s_w == kStagesW8) { s_w = 0; ph_w ^= 1u; }
+                if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
             }
         }
     }

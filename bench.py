@@ -31,8 +31,9 @@ if str(ROOT) not in sys.path:
 
 L2_BYTES = 126 * 1024 * 1024
 # dram bytes (read + write) of one launch of the dominant kernel from an ncu capture of this
-# workload; None until a capture has been taken (summaries under profiles/).
-NCU_TRAFFIC_BYTES = {"int8_channel": None, "fp8_tensor": None, "int8_group": None}
+# workload (profiles/quant_segments_int8_channel_8192x8192.md: 134.2 MB read + 29.0 MB written; the
+# rest of the 67 MB of codes was still dirty in the 126 MB L2 when the captured launch ended).
+NCU_TRAFFIC_BYTES = {"int8_channel": 163_215_616, "fp8_tensor": None, "int8_group": None}
 
 
 def _peaks():
@@ -375,6 +376,30 @@ def run_reference(args, rank, world):
     """CPU formulation of the same step on this host's cores (rank 0 only; other ranks do nothing)."""
     if rank != 0:
         return
+    torch.set_num_threads(os.cpu_count() or 1)  # launchers such as torchrun pin OMP_NUM_THREADS=1
+    if args.workload == "w8a16":
+        from cublade_b200 import workloads as W
+        from oracle import oracle as O
+
+        M = min(args.m, 64)
+        w, x, _ = W.w8a16_case(M)
+        lay = O.w8a16_quantize(w, torch.bfloat16)
+        O.w8a16_forward(x, lay)
+        steps = max(1, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.w8a16_forward(x, lay)
+        dt = (time.perf_counter() - t0) / steps
+        v = 2.0 * M * 14336 * 4096 / dt / 1e12
+        sample = f"first {M} of {args.m} activation rows per step (reference CPU branch of the layer), {steps} steps"
+        print(json.dumps({"impl": "reference", "metric": "W8A16 TFLOPS", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+                          "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"w8a16_linear M={args.m} N=14336 K=4096"},
+                          "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                           "sample": sample},
+                          "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
     wl = WORKLOADS[args.workload](None)
     if args.workload == "fp8_sharded":  # bounded sample: one 2^27-element chunk, scaled to the metric's unit
         wl.bytes_per_step = wl.CHUNK * 8
@@ -400,7 +425,116 @@ def run_reference(args, rank, world):
     }))
 
 
+def run_w8a16(args, rank, world, local_rank, device, dist):
+    """--workload w8a16: the W8A16 linear of the benchmark configuration (N=14336, K=4096, int8 weights
+    quantized per output channel from N(0, 0.02), bf16 activations N(0,1)), M = --m rows.  A step is
+    one forward.  With N > 1 ranks the output features are sharded (strong scaling, no collective)."""
+    import cublade_b200 as cb
+    from cublade_b200 import _native as N
+    from cublade_b200 import workloads as W
+    from cublade_b200.sharding import shard_range
+
+    peaks = _peaks()
+    M, N_, K_ = args.m, 14336, 4096
+    w, x_host, _ = W.w8a16_case(M)
+    n0, n1 = shard_range(N_, rank, world)
+    layer = cb.cuBladeW8A16LinearLayer(K_, n1 - n0, bias=False, dtype=torch.bfloat16)
+    layer.quantize(w[n0:n1].to(device))
+    layer = layer.to(device)
+    x_pinned = x_host.pin_memory()
+    y_pinned = torch.empty(M, n1 - n0, dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(device)
+    warmup, K = max(args.warmup, 3), args.steps
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        layer(x)
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            y_static = layer(x)
+    for _ in range(warmup):
+        g.replay()
+    barrier()
+    launches0 = N.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(K):
+            g.replay()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1) / K
+    # end to end: activations from pinned host memory, result back to the host
+    for _ in range(3):
+        layer(x_pinned.to(device, non_blocking=True))
+    barrier()
+    steps_e2e = max(3, min(K, 20))
+    e0.record()
+    for _ in range(steps_e2e):
+        y = layer(x_pinned.to(device, non_blocking=True))
+        y_pinned.copy_(y, non_blocking=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / steps_e2e
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0].item()), float(t[1].item())
+    if rank != 0:
+        return
+    flops = 2.0 * M * N_ * K_
+    tf = flops / (ms * 1e-3) / 1e12
+    local_tf = tf / world
+    bytes_local = (n1 - n0) * K_ + 2 * (n1 - n0) + 2 * M * K_ + 2 * M * (n1 - n0)
+    tensor_bound = M >= 1024
+    roof = ({"bound": "tensor", "achieved": local_tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+             "frac": local_tf / peaks["bf16_tflops_sustained"], "frac_of_burst_peak": local_tf / peaks["bf16_tflops"],
+             "peak_note": "sustained cuBLAS bf16 figure: the kernel is timed back to back inside a long loop"}
+            if tensor_bound else
+            {"bound": "hbm", "achieved": bytes_local / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+             "frac": bytes_local / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
+    roof.update({"kernel": "w8a16_tc_kernel (tcgen05/TMEM)" if M >= 65 else "w8a16_stream_kernel", "traffic": None,
+                 "peak_source": peaks["source"], "avg_launch_us": ms * 1e3})
+    out = {"metric": "W8A16 TFLOPS", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": warmup,
+           "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+           "data": "synthetic",
+           "config": {"workload": f"w8a16_linear M={M} N={N_} K={K_} int8 per-output-channel weights, bf16 activations",
+                      "l2_policy": "back-to-back replays; weights (58.7 MB) + activations stay L2-resident, the shape is "
+                                   "tensor-bound" if tensor_bound else "back-to-back replays (L2-resident weights)",
+                      "launch": "one CUDA graph per step", "seed": 3, "sharding": f"output features over {world} rank(s)"},
+           "clocks": clocks.summary(),
+           "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K_ * 2,
+                   "d2h_bytes_per_step": M * (n1 - n0) * 2, "ms_per_step": e2e_ms, "steps": steps_e2e},
+           "gpu_launches": K, "gpu_launches_note": "1 kernel of libcublade_b200.so per step, replayed from a CUDA graph",
+           "roofline": roof}
+    if not args.no_cpu_baseline:
+        # the reference's own CPU branch of the layer (x @ W.t() in the activation dtype), bounded sample
+        from oracle import oracle as O
+
+        torch.set_num_threads(os.cpu_count() or 1)
+        ms_cpu = min(M, 64)
+        lay = O.w8a16_quantize(w, torch.bfloat16)
+        xs = x_host[:ms_cpu]
+        O.w8a16_forward(xs, lay)
+        t0 = time.perf_counter()
+        O.w8a16_forward(xs, lay)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": 2.0 * ms_cpu * N_ * K_ / dt / 1e12, "unit": "TFLOP/s",
+                               "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"first {ms_cpu} activation rows, one forward after one warm-up "
+                                         "(reference CPU branch of the layer)"}
+    print(json.dumps(out))
+
+
 def cpu_baseline(wl, budget_s=12.0):
+    torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
     x = wl.cpu_input()
     wl.cpu_step(x)  # warm-up
@@ -424,7 +558,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS) + ["w8a16"])
+    ap.add_argument("--m", type=int, default=2048, help="activation rows for --workload w8a16")
     ap.add_argument("--impl", default="cublade_b200", choices=["cublade_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-w8a16", action="store_true", help="skip the W8A16 TFLOP/s table")
@@ -451,6 +586,12 @@ def main():
     from cublade_b200 import _native as N
 
     N.lib()  # fail loudly if the extension is missing
+    if args.workload == "w8a16":
+        run_w8a16(args, rank, world, local_rank, device, dist)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     warmup = max(args.warmup, 3)
     if args.workload == "fp8_sharded":
         wl = Fp8ShardedWorkload(device, world=world, rank=rank)

@@ -85,7 +85,7 @@ struct TcParams {
     unsigned int* error_flag;  // global; set to 1 when a bounded wait expired
 };
 
-constexpr int kMaxKO = 32;  // outlier columns handled by the epilogue's CUDA-core side product
+constexpr int kMaxKO = 64;  // outlier columns handled by the epilogue's CUDA-core side product
 
 template <typename A>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -224,12 +224,6 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const bool n_ok = n < p.N;
             const float scale = n_ok ? load_scalar(p.scales, p.scales_dtype, n) : 0.0f;
             const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
-            float wo_row[kMaxKO];
-            if (p.KO > 0) {
-#pragma unroll
-                for (int j = 0; j < kMaxKO; ++j)
-                    wo_row[j] = (n_ok && j < p.KO) ? Widen<A>::to_float(wo[n * p.KO + j]) : 0.0f;
-            }
             {
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
@@ -247,11 +241,13 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const int64_t m = m_base + c0 + c;
                     if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
                     float v = __uint_as_float(r[c]) * scale;
-                    if (p.KO > 0) {
-                        const A* xrow = xo + m * p.ldxo;  // same address in every lane: broadcast load
-#pragma unroll
-                        for (int j = 0; j < kMaxKO; ++j)
-                            if (j < p.KO) v = fmaf(Widen<A>::to_float(__ldg(xrow + j)), wo_row[j], v);
+                    if (p.KO > 0 && n_ok) {
+                        // side product over the outlier columns: the activation row is the same address
+                        // in every lane (broadcast load), the weight row is this lane's own
+                        const A* xrow = xo + m * p.ldxo;
+                        const A* wrow = wo + n * p.KO;
+                        for (int j = 0; j < (int)p.KO; ++j)
+                            v = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), v);
                     }
                     v += bias;
                     if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);

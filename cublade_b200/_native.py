@@ -30,6 +30,7 @@ SIGNATURES = {
     "cb_version": (c_int32, []),
     "cb_last_error": (c_char_p, []),
     "cb_launch_count": (c_int64, []),
+    "cb_per_tensor_scratch_floats": (c_int32, []),
     "cb_quantize_per_tensor_fp8": (c_int32, [c_void_p, c_int32, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_dequantize_per_tensor_fp8": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_void_p]),
     "cb_quantize_per_tensor_int8": (c_int32, [c_void_p, c_int32, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -83,6 +84,17 @@ def lib() -> ctypes.CDLL:
             fn.argtypes = args
         _lib = handle
     return _lib
+
+
+_scratch_floats = None
+
+
+def per_tensor_scratch_floats() -> int:
+    """Floats of device scratch the one-call per-tensor quantizers need."""
+    global _scratch_floats
+    if _scratch_floats is None:
+        _scratch_floats = int(lib().cb_per_tensor_scratch_floats())
+    return _scratch_floats
 
 
 def dtype_code(dt: torch.dtype) -> int:

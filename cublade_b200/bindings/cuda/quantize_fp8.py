@@ -26,7 +26,7 @@ def quantize_per_tensor_fp8(x: torch.Tensor, eps: float = 1e-12) -> tuple[torch.
     with N.device_guard(x):
         q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
         scale = torch.empty((), dtype=torch.float32, device=x.device)
-        amax = torch.empty((), dtype=torch.float32, device=x.device)
+        amax = torch.empty(N.per_tensor_scratch_floats(), dtype=torch.float32, device=x.device)
         N.check(N.lib().cb_quantize_per_tensor_fp8(x.data_ptr(), N.dtype_code(x.dtype), x.numel(), float(eps),
                                                    q.data_ptr(), scale.data_ptr(), amax.data_ptr(), N.stream_ptr(x)))
     return q, scale

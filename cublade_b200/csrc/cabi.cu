@@ -36,11 +36,16 @@ int32_t quantize_per_tensor(const char* name, const void* x, int32_t dtype, int6
                             float* scale, float* amax, void* stream) {
     if (!scale || !amax || n < 0 || (n > 0 && (!x || !q))) return fail(CB_ERR_ARGUMENT, "%s: null pointer or n < 0", name);
     cudaStream_t s = as_stream(stream);
-    cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+    // phase 1 writes one partial maximum per CTA into the scratch (no atomics, nothing to zero),
+    // phase 2 folds them; for n == 0 the single slot is cleared so the scale is that of amax = 0
+    int nparts = 0;
+    cudaError_t e = cb::launch_amax_partials(x, dtype, n, amax, &nparts, s);
     if (e != cudaSuccess) return cuda_result(e, name, 0);
-    e = cb::launch_amax_tensor(x, dtype, n, amax, s);
-    if (e != cudaSuccess) return cuda_result(e, name, 0);
-    e = cb::launch_cast_tensor(x, dtype, n, amax, eps, code, q, scale, s);
+    if (nparts == 0) {
+        e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+        if (e != cudaSuccess) return cuda_result(e, name, 0);
+    }
+    e = cb::launch_cast_tensor(x, dtype, n, amax, nparts, eps, code, q, scale, s);
     return cuda_result(e, name, n > 0 ? 2 : 1);
 }
 
@@ -51,6 +56,8 @@ extern "C" {
 int32_t cb_version(void) { return 100; }
 const char* cb_last_error(void) { return g_err; }
 int64_t cb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int32_t cb_per_tensor_scratch_floats(void) { return cb::per_tensor_scratch_floats(); }
 
 int32_t cb_quantize_per_tensor_fp8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
                                    float* amax_scratch, void* stream) {
@@ -82,7 +89,7 @@ int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float*
         return fail(CB_ERR_DTYPE, "cb_cast_per_tensor: e4m3 needs float16 or bfloat16 input");
     if (!amax || !scale || n < 0 || (n > 0 && (!x || !q)))
         return fail(CB_ERR_ARGUMENT, "cb_cast_per_tensor: null pointer or n < 0");
-    return cuda_result(cb::launch_cast_tensor(x, dtype, n, amax, eps, code_kind, q, scale, as_stream(stream)),
+    return cuda_result(cb::launch_cast_tensor(x, dtype, n, amax, 0, eps, code_kind, q, scale, as_stream(stream)),
                        "cb_cast_per_tensor", 1);
 }
 

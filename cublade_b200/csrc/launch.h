@@ -21,8 +21,13 @@ int sm_count();
 // amax[0] = max(amax[0], max|x|); amax must hold a non-negative float (0 to start).
 cudaError_t launch_amax_tensor(const void* x, int dtype, int64_t n, float* amax, cudaStream_t s);
 // codes = encode(x * qmax/max(amax,eps)); scale_out[0] = 1/(qmax/max(amax,eps)).
-cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float* amax, float eps, int code,
+// nparts == 0: amax is one float; nparts > 0: amax points at nparts per-CTA partial maxima to fold.
+cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float* amax, int nparts, float eps, int code,
                                void* q, float* scale_out, cudaStream_t s);
+// Single-GPU phase 1 without atomics or pre-zeroing: partials[i] = max|x| seen by CTA i, *nparts = CTAs used
+// (<= per_tensor_scratch_floats()).
+int per_tensor_scratch_floats();
+cudaError_t launch_amax_partials(const void* x, int dtype, int64_t n, float* partials, int* nparts, cudaStream_t s);
 
 // ---- per-segment (rows of a [nseg, L] matrix: channels or groups), one pass --
 cudaError_t launch_quant_segments(const void* x, int dtype, int64_t nseg, int64_t L, float eps, int code, void* q,

@@ -289,6 +289,13 @@ __device__ __forceinline__ InvScale inv_and_scale(float amax, float eps) {
     return r;
 }
 
+// 256-bit global store (sm_100): one full 32-byte sector per thread per instruction.
+__device__ __forceinline__ void st_stream32(void* p, const uint4& lo, const uint4& hi) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                 "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
+}
+
 // Streaming 128-bit / 64-bit / 32-bit global accesses.
 __device__ __forceinline__ uint4 ld_stream16(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint4 ld_keep16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }

@@ -53,7 +53,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // quantize_int8.cu:47-101)
 // A CTA iteration covers one contiguous chunk of kBlock*4 packs (16 KiB).
 // ===========================================================================
-template <typename T>
+template <typename T, bool PARTIALS>
 __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict__ x, int64_t n,
                                                              float* __restrict__ amax) {
     constexpr int E = DTypeTraits<T>::kLanes;
@@ -88,11 +88,16 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
     }
     __shared__ float red[kBlock / 32];
     float m = block_max(am.finish(), red);
-    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
+    if (threadIdx.x == 0) {
+        // PARTIALS: one slot per CTA, no atomics and nothing to pre-zero (the cast kernel folds the
+        // slots); otherwise an integer atomicMax on the bit pattern of a non-negative float.
+        if constexpr (PARTIALS) amax[blockIdx.x] = m;
+        else atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
+    }
 }
 
 // any alignment
-template <typename T>
+template <typename T, bool PARTIALS>
 __global__ void __launch_bounds__(kBlock) amax_tensor_scalar_kernel(const T* __restrict__ x, int64_t n,
                                                                     float* __restrict__ amax) {
     float m = 0.0f;
@@ -100,7 +105,18 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_scalar_kernel(const T* __r
         m = fmaxf(m, fabsf(DTypeTraits<T>::to_float(x[i])));
     __shared__ float red[kBlock / 32];
     m = block_max(m, red);
-    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
+    if (threadIdx.x == 0) {
+        if constexpr (PARTIALS) amax[blockIdx.x] = m;
+        else atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
+    }
+}
+
+// amax for the cast kernels: amax[0] when nparts == 0, else the max over nparts per-CTA partials
+__device__ __forceinline__ float fold_amax(const float* __restrict__ amax, int nparts, float* red) {
+    if (nparts <= 0) return __ldg(amax);
+    float m = 0.0f;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) m = fmaxf(m, __ldg(amax + i));
+    return block_max(m, red);
 }
 
 // ===========================================================================
@@ -109,11 +125,12 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_scalar_kernel(const T* __r
 // ===========================================================================
 template <typename T, typename Code>
 __global__ void __launch_bounds__(kBlock) cast_tensor_kernel(const T* __restrict__ x, int64_t n,
-                                                             const float* __restrict__ amax, float eps,
+                                                             const float* __restrict__ amax, int nparts, float eps,
                                                              uint8_t* __restrict__ q, float* __restrict__ scale_out) {
     constexpr int E = DTypeTraits<T>::kLanes;
     constexpr int kChunkPacks = kBlock * 4;
-    const InvScale is = inv_and_scale<Code>(__ldg(amax), eps);
+    __shared__ float red_amax[kBlock / 32];
+    const InvScale is = inv_and_scale<Code>(fold_amax(amax, nparts, red_amax), eps);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = is.scale;
     const int64_t npk = n / E;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
@@ -145,10 +162,11 @@ __global__ void __launch_bounds__(kBlock) cast_tensor_kernel(const T* __restrict
 
 template <typename T, typename Code>
 __global__ void __launch_bounds__(kBlock) cast_tensor_scalar_kernel(const T* __restrict__ x, int64_t n,
-                                                                    const float* __restrict__ amax, float eps,
-                                                                    uint8_t* __restrict__ q,
+                                                                    const float* __restrict__ amax, int nparts,
+                                                                    float eps, uint8_t* __restrict__ q,
                                                                     float* __restrict__ scale_out) {
-    const InvScale is = inv_and_scale<Code>(__ldg(amax), eps);
+    __shared__ float red_amax[kBlock / 32];
+    const InvScale is = inv_and_scale<Code>(fold_amax(amax, nparts, red_amax), eps);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = is.scale;
     for (int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (int64_t)gridDim.x * kBlock)
         q[i] = Code::encode1(__fmul_rn(DTypeTraits<T>::to_float(x[i]), is.inv));
@@ -295,6 +313,53 @@ __global__ void __launch_bounds__(kBlock) dequant_kernel(const uint8_t* __restri
     }
 }
 
+// Same, 16 codes per thread per step: one 128-bit load of codes, one 256-bit store of 16-bit values
+// (a full 32-byte sector per thread per store instruction).  Needs n and seg_len to be multiples
+// of 16 apart from a scalar tail, q 16-byte and y 32-byte aligned.
+template <typename OutT, typename Code, int SEG>
+__global__ void __launch_bounds__(kBlock) dequant16_kernel(const uint8_t* __restrict__ q,
+                                                           const float* __restrict__ scale, int64_t n,
+                                                           int64_t pps /* 16-packs per segment, or shift */,
+                                                           int64_t seg_len, OutT* __restrict__ y) {
+    constexpr int kChunkPacks = kBlock * 4;
+    const int64_t npk = n / 16;
+    const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
+    const uint4* qp = reinterpret_cast<const uint4*>(q);
+    float s0 = 0.0f;
+    if constexpr (SEG == 0) s0 = __ldg(scale);
+    for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const int64_t p0 = c * kChunkPacks + threadIdx.x;
+        uint4 v[4];
+        float s[4];
+        bool ok[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t p = p0 + k * kBlock;
+            ok[k] = p < npk;
+            if (ok[k]) {
+                v[k] = ld_stream16(qp + p);
+                if constexpr (SEG == 0) s[k] = s0;
+                else if constexpr (SEG == 1) s[k] = __ldg(scale + (p >> pps));
+                else s[k] = __ldg(scale + (p / pps));
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (!ok[k]) continue;
+            const uint4 lo = codes_decode8<OutT, Code>(make_uint2(v[k].x, v[k].y), s[k]);
+            const uint4 hi = codes_decode8<OutT, Code>(make_uint2(v[k].z, v[k].w), s[k]);
+            st_stream32(y + (p0 + k * kBlock) * 16, lo, hi);
+        }
+    }
+    if (blockIdx.x == 0) {  // fewer than 16 trailing codes
+        const int64_t t = npk * 16 + threadIdx.x;
+        if (t < n) {
+            const float st = __ldg(scale + (seg_len > 0 ? t / seg_len : 0));
+            y[t] = DTypeTraits<OutT>::from_float(__fmul_rn(Code::decode1(q[t]), st));
+        }
+    }
+}
+
 template <typename OutT, typename Code>
 __global__ void __launch_bounds__(kBlock) dequant_scalar_kernel(const uint8_t* __restrict__ q,
                                                                 const float* __restrict__ scale, int64_t n,
@@ -316,59 +381,75 @@ static inline int persistent_grid(int64_t work_items, int ctas_per_sm) {
     return (int)(g < 1 ? 1 : g);
 }
 
+// grid of the amax kernel for n elements (= number of partial slots it writes in PARTIALS mode)
 template <typename T>
-static cudaError_t amax_tensor_t(const void* x, int64_t n, float* amax, cudaStream_t s) {
+static int amax_grid(const void* x, int64_t n) {
     constexpr int E = DTypeTraits<T>::kLanes;
+    if (aligned(x, 16)) return persistent_grid((n / E + kBlock * 4 - 1) / (kBlock * 4), 8);
+    return persistent_grid((n + kBlock - 1) / kBlock, 8);
+}
+
+template <typename T, bool PARTIALS>
+static cudaError_t amax_tensor_t(const void* x, int64_t n, float* amax, int* nparts, cudaStream_t s) {
+    if (nparts) *nparts = 0;
     if (n <= 0) return cudaSuccess;
-    if (aligned(x, 16)) {
-        const int64_t nchunks = (n / E + kBlock * 4 - 1) / (kBlock * 4);
-        amax_tensor_kernel<T><<<persistent_grid(nchunks, 8), kBlock, 0, s>>>(static_cast<const T*>(x), n, amax);
-    } else {
-        amax_tensor_scalar_kernel<T><<<persistent_grid((n + kBlock - 1) / kBlock, 8), kBlock, 0, s>>>(
-            static_cast<const T*>(x), n, amax);
-    }
+    const int grid = amax_grid<T>(x, n);
+    if (nparts) *nparts = grid;
+    if (aligned(x, 16)) amax_tensor_kernel<T, PARTIALS><<<grid, kBlock, 0, s>>>(static_cast<const T*>(x), n, amax);
+    else amax_tensor_scalar_kernel<T, PARTIALS><<<grid, kBlock, 0, s>>>(static_cast<const T*>(x), n, amax);
     return cudaPeekAtLastError();
 }
 
 cudaError_t launch_amax_tensor(const void* x, int dtype, int64_t n, float* amax, cudaStream_t s) {
     switch (dtype) {
-        case kF16: return amax_tensor_t<__half>(x, n, amax, s);
-        case kBF16: return amax_tensor_t<__nv_bfloat16>(x, n, amax, s);
-        case kF32: return amax_tensor_t<float>(x, n, amax, s);
+        case kF16: return amax_tensor_t<__half, false>(x, n, amax, nullptr, s);
+        case kBF16: return amax_tensor_t<__nv_bfloat16, false>(x, n, amax, nullptr, s);
+        case kF32: return amax_tensor_t<float, false>(x, n, amax, nullptr, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+int per_tensor_scratch_floats() { return sm_count() * 8; }
+
+cudaError_t launch_amax_partials(const void* x, int dtype, int64_t n, float* partials, int* nparts, cudaStream_t s) {
+    switch (dtype) {
+        case kF16: return amax_tensor_t<__half, true>(x, n, partials, nparts, s);
+        case kBF16: return amax_tensor_t<__nv_bfloat16, true>(x, n, partials, nparts, s);
+        case kF32: return amax_tensor_t<float, true>(x, n, partials, nparts, s);
     }
     return cudaErrorInvalidValue;
 }
 
 template <typename T, typename Code>
-static cudaError_t cast_tensor_t(const void* x, int64_t n, const float* amax, float eps, void* q, float* scale_out,
-                                 cudaStream_t s) {
+static cudaError_t cast_tensor_t(const void* x, int64_t n, const float* amax, int nparts, float eps, void* q,
+                                 float* scale_out, cudaStream_t s) {
     constexpr int E = DTypeTraits<T>::kLanes;
     // n == 0 still writes the scale (amax 0 -> eps), as the reference's launch of an empty grid would not;
     // the host layer never calls with n == 0, keep one CTA so scale_out is defined.
     if (aligned(x, 16) && aligned(q, 8)) {
         const int64_t nchunks = (n / E + kBlock * 4 - 1) / (kBlock * 4);
         cast_tensor_kernel<T, Code><<<persistent_grid(nchunks, 8), kBlock, 0, s>>>(
-            static_cast<const T*>(x), n, amax, eps, static_cast<uint8_t*>(q), scale_out);
+            static_cast<const T*>(x), n, amax, nparts, eps, static_cast<uint8_t*>(q), scale_out);
     } else {
         cast_tensor_scalar_kernel<T, Code><<<persistent_grid((n + kBlock - 1) / kBlock, 8), kBlock, 0, s>>>(
-            static_cast<const T*>(x), n, amax, eps, static_cast<uint8_t*>(q), scale_out);
+            static_cast<const T*>(x), n, amax, nparts, eps, static_cast<uint8_t*>(q), scale_out);
     }
     return cudaPeekAtLastError();
 }
 
-cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float* amax, float eps, int code, void* q,
-                               float* scale_out, cudaStream_t s) {
+cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float* amax, int nparts, float eps, int code,
+                               void* q, float* scale_out, cudaStream_t s) {
     if (code == kCodeE4M3) {
         switch (dtype) {
-            case kF16: return cast_tensor_t<__half, E4M3Code>(x, n, amax, eps, q, scale_out, s);
-            case kBF16: return cast_tensor_t<__nv_bfloat16, E4M3Code>(x, n, amax, eps, q, scale_out, s);
-            case kF32: return cast_tensor_t<float, E4M3Code>(x, n, amax, eps, q, scale_out, s);
+            case kF16: return cast_tensor_t<__half, E4M3Code>(x, n, amax, nparts, eps, q, scale_out, s);
+            case kBF16: return cast_tensor_t<__nv_bfloat16, E4M3Code>(x, n, amax, nparts, eps, q, scale_out, s);
+            case kF32: return cast_tensor_t<float, E4M3Code>(x, n, amax, nparts, eps, q, scale_out, s);
         }
     } else if (code == kCodeInt8) {
         switch (dtype) {
-            case kF16: return cast_tensor_t<__half, Int8CodeClamped>(x, n, amax, eps, q, scale_out, s);
-            case kBF16: return cast_tensor_t<__nv_bfloat16, Int8CodeClamped>(x, n, amax, eps, q, scale_out, s);
-            case kF32: return cast_tensor_t<float, Int8CodeClamped>(x, n, amax, eps, q, scale_out, s);
+            case kF16: return cast_tensor_t<__half, Int8CodeClamped>(x, n, amax, nparts, eps, q, scale_out, s);
+            case kBF16: return cast_tensor_t<__nv_bfloat16, Int8CodeClamped>(x, n, amax, nparts, eps, q, scale_out, s);
+            case kF32: return cast_tensor_t<float, Int8CodeClamped>(x, n, amax, nparts, eps, q, scale_out, s);
         }
     }
     return cudaErrorInvalidValue;
@@ -450,6 +531,23 @@ static cudaError_t dequant_t(const void* q, const float* scale, int64_t n, int64
     if (!vec_ok) {
         dequant_scalar_kernel<OutT, Code><<<persistent_grid((n + kBlock - 1) / kBlock, 8), kBlock, 0, s>>>(
             qp, scale, n, seg_len, yp);
+        return cudaPeekAtLastError();
+    }
+    if (aligned(q, 16) && aligned(y, 32) && (seg_len == 0 || seg_len % 16 == 0)) {
+        const int64_t nchunks16 = (n / 16 + kBlock * 4 - 1) / (kBlock * 4);
+        const int grid16 = persistent_grid(nchunks16, 8);
+        if (seg_len == 0) {
+            dequant16_kernel<OutT, Code, 0><<<grid16, kBlock, 0, s>>>(qp, scale, n, 0, 0, yp);
+        } else {
+            const int64_t pps = seg_len / 16;
+            if ((pps & (pps - 1)) == 0) {
+                int shift = 0;
+                while ((int64_t(1) << shift) < pps) ++shift;
+                dequant16_kernel<OutT, Code, 1><<<grid16, kBlock, 0, s>>>(qp, scale, n, shift, seg_len, yp);
+            } else {
+                dequant16_kernel<OutT, Code, 2><<<grid16, kBlock, 0, s>>>(qp, scale, n, pps, seg_len, yp);
+            }
+        }
         return cudaPeekAtLastError();
     }
     const int64_t nchunks = (n / 8 + kBlock * 4 - 1) / (kBlock * 4);

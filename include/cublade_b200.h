@@ -50,9 +50,11 @@ int64_t cb_launch_count(void);
  *   cublade/kernels/cuda/quantization/quantize_per_tensor_fp8.cu:162-188
  *   (binding cublade/bindings/cuda/quantize_fp8.py:15-34)
  * x: n elements of CB_F16 / CB_BF16.  q: n bytes (e4m3 codes).  scale: fp32[1].
- * amax_scratch: fp32[1] device scratch, overwritten.
+ * amax_scratch: device scratch of cb_per_tensor_scratch_floats() floats, overwritten (one partial
+ * maximum per CTA of the first pass; no atomics, nothing to pre-zero).
  * scale = 1 / (448 / max(amax, eps)); q = e4m3_rn_satfinite(float(x) * (448 / max(amax, eps))).
  * ------------------------------------------------------------------------ */
+int32_t cb_per_tensor_scratch_floats(void);
 int32_t cb_quantize_per_tensor_fp8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
                                    float* amax_scratch, void* stream);
 
@@ -69,7 +71,7 @@ int32_t cb_dequantize_per_tensor_fp8(const void* q, const float* scale, int64_t 
  * ------------------------------------------------------------------------ */
 /* replaces quantize_per_tensor_int8(x, eps)
  *   cublade/kernels/cuda/quantization/quantize_int8.cu:470-484 (binding quantize_int8.py:18-38)
- * x: CB_F16 / CB_BF16 / CB_F32. */
+ * x: CB_F16 / CB_BF16 / CB_F32.  amax_scratch as for the FP8 call. */
 int32_t cb_quantize_per_tensor_int8(const void* x, int32_t dtype, int64_t n, float eps, void* q, float* scale,
                                     float* amax_scratch, void* stream);
 

@@ -170,7 +170,7 @@ def test_outputs_stay_inside_their_buffers():
         x = (torch.randn(n, generator=torch.Generator().manual_seed(n)) * 3).to(torch.bfloat16).cuda()
         qbuf = torch.full((n + 2 * pad,), 0x5A, dtype=torch.uint8, device="cuda")
         sbuf = torch.full((3,), 7.25, dtype=torch.float32, device="cuda")
-        amax = torch.zeros(1, dtype=torch.float32, device="cuda")
+        amax = torch.empty(N.per_tensor_scratch_floats(), dtype=torch.float32, device="cuda")
         N.check(L.cb_quantize_per_tensor_fp8(x.data_ptr(), N.CB_BF16, n, 1e-12, qbuf.data_ptr() + pad,
                                              sbuf.data_ptr() + 4, amax.data_ptr(), stream))
         torch.cuda.synchronize()

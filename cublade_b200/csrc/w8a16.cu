@@ -12,7 +12,7 @@ cudaError_t launch_w8a16_tc_pair(const W8A16Args& a, cudaStream_t s);
 bool w8a16_tc_pair_supported(const W8A16Args& a);
 
 // Rows of activations from which the tensor-core kernels are used when the shape allows it.
-constexpr int64_t kTcMinM = 65;
+constexpr int64_t kTcMinM = 17;  // measured: the streaming kernel wins up to 16 rows, the tensor-core kernel from 17
 
 size_t w8a16_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
 

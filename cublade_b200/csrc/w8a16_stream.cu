@@ -319,6 +319,157 @@ __global__ void __launch_bounds__(kWarps * 32) w8a16_stream_kernel(const StreamP
     }
 }
 
+// Fast path of the same kernel for the common aligned case: K a multiple of 64, N a multiple of 16,
+// 16-byte aligned rows.  No bounds checks or 64-bit index arithmetic inside the k loop: pointers
+// are set up once and advanced by constants, rows beyond M are handled by a loop-invariant
+// predicate.  Everything else (operand orientation, k permutation, two-stage software pipeline,
+// 4-way split of K, epilogue) is as in w8a16_stream_kernel.
+template <typename A, int MT>
+__global__ void __launch_bounds__(kWarps * 32, 7) w8a16_stream_fast_kernel(const StreamParams p) {
+    // Seven CTAs per SM (<= 72 registers per thread) so that the N / 16 tiles of the usual layer
+    // shapes are all resident at once: with fewer, a short second wave of CTAs doubles the run time.
+    // Only the weight stream is staged in registers (two stages of two 64-k rounds); the
+    // activations are read where they are used, they are served by L1.
+    constexpr int U = 2;  // rounds (64 k each) per pipeline stage
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n0 = (int64_t)blockIdx.x * 16;
+
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    // 16-byte units: a round of a weight row is 4 units (thread t takes unit t), of an activation
+    // row 8 units (thread t takes units 2t, 2t+1)
+    const uint4* w0 = reinterpret_cast<const uint4*>(p.wq + (n0 + g) * p.K) + t;
+    const uint4* w1 = reinterpret_cast<const uint4*>(p.wq + (n0 + g + 8) * p.K) + t;
+    const uint4* xr[MT];
+    bool m_ok[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int64_t m = p.m0 + mt * 8 + g;
+        m_ok[mt] = m < p.M;
+        xr[mt] = reinterpret_cast<const uint4*>(static_cast<const A*>(p.x) + (m_ok[mt] ? m : 0) * p.ldx) + 2 * t;
+    }
+    const int nrounds = (int)(p.K / 64);
+
+    struct Stage {
+        uint4 c0[U], c1[U];
+    };
+    auto load_stage = [&](Stage& st, int r) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (r + u < nrounds) {
+                st.c0[u] = __ldcs(w0 + (r + u) * 4);
+                st.c1[u] = __ldcs(w1 + (r + u) * 4);
+            }
+        }
+    };
+    auto compute_stage = [&](const Stage& st, int r) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (r + u >= nrounds) continue;
+            uint4 xa[MT][2];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                if (m_ok[mt]) {
+                    xa[mt][0] = __ldg(xr[mt] + (r + u) * 8);
+                    xa[mt][1] = __ldg(xr[mt] + (r + u) * 8 + 1);
+                } else {
+                    xa[mt][0] = make_uint4(0u, 0u, 0u, 0u);
+                    xa[mt][1] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            const uint32_t cw0[4] = {st.c0[u].x, st.c0[u].y, st.c0[u].z, st.c0[u].w};
+            const uint32_t cw1[4] = {st.c1[u].x, st.c1[u].y, st.c1[u].z, st.c1[u].w};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                uint32_t a[4];
+                Act<A>::widen4(cw0[s], a[0], a[2]);
+                Act<A>::widen4(cw1[s], a[1], a[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint4& xq = xa[mt][s >> 1];
+                    const uint32_t b0 = (s & 1) ? xq.z : xq.x, b1 = (s & 1) ? xq.w : xq.y;
+                    Act<A>::mma(acc[mt], a, b0, b1);
+                }
+            }
+        }
+    };
+    {
+        Stage st0, st1;
+        int r = warp * U;
+        constexpr int step = kWarps * U;
+        load_stage(st0, r);
+        while (r < nrounds) {
+            load_stage(st1, r + step);
+            compute_stage(st0, r);
+            r += step;
+            if (r >= nrounds) break;
+            load_stage(st0, r + step);
+            compute_stage(st1, r);
+            r += step;
+        }
+    }
+
+    const float s0 = load_as_float(p.scales, p.scales_dtype, n0 + g);
+    const float s1 = load_as_float(p.scales, p.scales_dtype, n0 + g + 8);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        acc[mt][0] *= s0; acc[mt][1] *= s0;
+        acc[mt][2] *= s1; acc[mt][3] *= s1;
+    }
+    if (p.KO > 0) {
+        const A* xo = static_cast<const A*>(p.xo);
+        const A* wo = static_cast<const A*>(p.wo);
+        const int64_t osteps = (p.KO + 15) / 16;
+        for (int64_t st = warp; st < osteps; st += kWarps) {
+            const int64_t k = st * 16 + t * 4;
+            uint32_t a0[2], a1[2];
+            load_acts<A, 1>(wo + (n0 + g) * p.KO, k, p.KO, true, a0);
+            load_acts<A, 1>(wo + (n0 + g + 8) * p.KO, k, p.KO, true, a1);
+            const uint32_t a[4] = {a0[0], a1[0], a0[1], a1[1]};
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int64_t m = p.m0 + mt * 8 + g;
+                uint32_t b[2];
+                load_acts<A, 1>(xo + m * p.ldxo, k, p.KO, m < p.M, b);
+                Act<A>::mma(acc[mt], a, b[0], b[1]);
+            }
+        }
+    }
+    __shared__ float red[kWarps - 1][MT * 4][32];
+    if (warp > 0) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red[warp - 1][mt * 4 + j][lane] = acc[mt][j];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int w = 0; w < kWarps - 1; ++w)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[mt][j] += red[w][mt * 4 + j][lane];
+    A* y = static_cast<A*>(p.y);
+    const float b0 = p.bias ? load_as_float(p.bias, p.bias_dtype, n0 + g) : 0.0f;
+    const float b1 = p.bias ? load_as_float(p.bias, p.bias_dtype, n0 + g + 8) : 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int64_t m = p.m0 + mt * 8 + 2 * t + j;
+            if (m >= p.M) continue;
+            y[m * p.ldy + n0 + g] = Act<A>::from_float(acc[mt][j] + b0);
+            y[m * p.ldy + n0 + g + 8] = Act<A>::from_float(acc[mt][2 + j] + b1);
+        }
+    }
+}
+
 template <typename Elem>
 __global__ void gather_cols_kernel(const Elem* __restrict__ src, int64_t M, int64_t ld_src,
                                    const int64_t* __restrict__ cols, int64_t ncols, Elem* __restrict__ dst,
@@ -357,8 +508,27 @@ cudaError_t stream_pick_mt(StreamParams p, cudaStream_t s) {
 }
 
 template <typename A>
+cudaError_t stream_fast(StreamParams p, cudaStream_t s) {
+    const unsigned grid = (unsigned)(p.N / 16);
+    int64_t m0 = 0;
+    while (m0 < p.M) {
+        const int64_t left = p.M - m0;
+        p.m0 = m0;
+        if (left > 8) {
+            w8a16_stream_fast_kernel<A, 2><<<grid, kWarps * 32, 0, s>>>(p);
+            m0 += 16;
+        } else {
+            w8a16_stream_fast_kernel<A, 1><<<grid, kWarps * 32, 0, s>>>(p);
+            m0 += 8;
+        }
+    }
+    return cudaPeekAtLastError();
+}
+
+template <typename A>
 cudaError_t stream_pick_vec(const StreamParams& p, cudaStream_t s) {
     const bool base16 = al(p.wq, 16) && al(p.x, 16);
+    if (base16 && p.M <= 16 && p.K % 64 == 0 && p.N % 16 == 0 && p.ldx % 8 == 0) return stream_fast<A>(p, s);
     if (base16 && p.K % 16 == 0 && p.ldx % 8 == 0) return stream_pick_mt<A, 16>(p, s);
     if (al(p.wq, 8) && al(p.x, 16) && p.K % 8 == 0 && p.ldx % 8 == 0) return stream_pick_mt<A, 8>(p, s);
     if (al(p.wq, 4) && al(p.x, 8) && p.K % 4 == 0 && p.ldx % 4 == 0) return stream_pick_mt<A, 4>(p, s);

@@ -53,15 +53,20 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     jobs = []
     for src in sources:
         obj = OBJ / (src.stem + ".o")
-        if force or _stale(obj, [src, *headers]):
-            flags = [f for f in NVCC_FLAGS if not (src.name in FMAD_OK and f == "-fmad=false")]
-            flags += os.environ.get("CB_EXTRA_NVCC_FLAGS", "").split()
+        flags = [f for f in NVCC_FLAGS if not (src.name in FMAD_OK and f == "-fmad=false")]
+        flags += os.environ.get("CB_EXTRA_NVCC_FLAGS", "").split()
+        # an object built with other flags is stale too: the flags it was built with sit beside it
+        stamp = obj.with_suffix(".flags")
+        same_flags = stamp.exists() and stamp.read_text() == " ".join(flags)
+        if force or verbose or not same_flags or _stale(obj, [src, *headers]):
             cmd = [nvcc, *flags, "-Xptxas", "-v" if verbose else "-O3", "-c", str(src), "-o", str(obj)]
-            jobs.append((src, cmd))
+            jobs.append((src, cmd, stamp, " ".join(flags)))
 
     def run(job):
-        src, cmd = job
+        src, cmd, stamp, flag_text = job
         r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode == 0:
+            stamp.write_text(flag_text)
         return src, r
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:

@@ -14,7 +14,13 @@ bool w8a16_tc_pair_supported(const W8A16Args& a);
 // Rows of activations from which the tensor-core kernels are used when the shape allows it.
 constexpr int64_t kTcMinM = 17;  // measured: the streaming kernel wins up to 16 rows, the tensor-core kernel from 17
 
-size_t w8a16_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+size_t w8a16_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+// Scratch for the split-K round of the single-CTA tensor-core kernel (0 when no shape of this
+// size would use it).  The kernels that do not need it ignore the pointer.
+size_t w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    return M >= kTcMinM ? w8a16_tc_workspace_bytes(M, N, K) : 0;
+}
 
 cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s) {
     if (path == 1) return launch_w8a16_stream(a, s);

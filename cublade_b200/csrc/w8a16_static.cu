@@ -110,7 +110,11 @@ int32_t cb_w8a16_linear_outlier_static(const void* x, int64_t M, int64_t K, int6
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.xo = KO > 0 ? xo : nullptr; a.wo = KO > 0 ? wo : nullptr; a.KO = KO; a.ldxo = ld_o;
     a.y = y; a.ldy = ldy; a.act_dtype = act_dtype;
-    a.workspace = nullptr; a.workspace_bytes = 0;
+    // what is left of the array behind the two re-packed buffers serves as the K-split workspace of the
+    // tensor-core kernel; when it is too small that kernel simply does not split
+    const size_t used = (need + 255u) & ~(size_t)255u;
+    a.workspace = used < kScratchBytes ? scratch + used : nullptr;
+    a.workspace_bytes = used < kScratchBytes ? kScratchBytes - used : 0;
     e = cb::launch_w8a16(a, 0, s);
     if (e != cudaSuccess) return fail(CB_ERR_CUDA, cudaGetErrorString(e));
     return CB_OK;

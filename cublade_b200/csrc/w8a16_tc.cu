@@ -1,5 +1,5 @@
 // W8A16 linear for tall activations: a tcgen05 / TMEM GEMM fed by TMA that widens int8 weight
-// tiles to 16-bit floats in shared memory.
+// tiles to 16-bit floats on the way to the tensor core.
 //
 //   y[m, n] = (sum_k x[m, k] * wq[n, k]) * scale[n] + sum_j xo[m, j] * wo[n, j] + bias[n]
 //
@@ -22,8 +22,15 @@
 //               the TMEM allocation (512 columns = two accumulators)
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, * scale, + outlier side product, + bias,
 //               round once, store; overlaps the next tile's main loop (double-buffered TMEM)
-//   warps 6-13  converters: int8 tile (shared) -> registers -> 16-bit in the canonical K-major
-//               128-byte-swizzled UMMA layout (shared), then fence.proxy.async + barrier arrive
+//   warps 6-13  converters: int8 tile (shared) -> registers -> 16-bit operand A, either in shared
+//               memory (canonical K-major 128-byte-swizzled UMMA layout, fence.proxy.async) or,
+//               for M <= 208, straight in tensor memory (tcgen05.st), then barrier arrive
+//
+// Schedule: tile t of round r goes to CTA t - r * gridDim.x.  A schedule without one full round
+// (fewer tiles than SMs) splits its tiles along K over the idle CTAs: every split stores its fp32
+// partial accumulator to its own slab of the workspace, and a small second kernel adds the slabs
+// of a tile in a fixed order and applies the ordinary epilogue (scale, outlier side product, bias,
+// one rounding).  Nobody waits for anybody, nothing is zeroed, and the result is deterministic.
 //
 // No TMA multicast, no clusters, no peer memory.  Every mbarrier wait is bounded: on expiry the
 // kernel raises an error flag in global memory, every role leaves its loop, TMEM is released and
@@ -32,6 +39,7 @@
 #include "tc_common.cuh"
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace cb {
@@ -40,33 +48,62 @@ namespace {
 
 using namespace tc;
 
-constexpr int kTileN = 128;     // weight rows (output features) per tile = UMMA M
-constexpr int kMaxTileX = 256;  // activation rows per tile = UMMA N (multiple of 16)
-constexpr int kStagesX = 4;     // activation tiles in flight (32 KiB each at 256 rows)
-constexpr int kStagesA = 3;     // converted weight tiles (16 KiB each)
-constexpr int kStagesW8 = 4;    // int8 weight tiles (8 KiB each)
+// Development switches (never in the shipped build): -DCB_TC_DEVTOOLS reads CB_TC_MODE / CB_TC_NOSPLIT
+// from the environment, -DCB_TC_PROFILE records per-CTA start / end times, -DCB_TC_NOCONVERT and
+// -DCB_TC_NOMMA leave out the widening arithmetic / the MMAs (wrong results, timing floors only).
+#ifdef CB_TC_NOCONVERT
+template <typename A>
+struct WidenDev {
+    __device__ __forceinline__ static void four(uint32_t c, uint32_t& lo, uint32_t& hi) { lo = c; hi = c; }
+};
+#define CB_WIDEN WidenDev
+#else
+#define CB_WIDEN Widen
+#endif
+
+constexpr int kTileN = 128;  // weight rows (output features) per tile = UMMA M
 constexpr int kConvWarps = 8;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = (3 + kEpiWarps + kConvWarps) * 32;  // + TMA(x), MMA, TMA(w8)
 constexpr int kW8Warp = 2 + kEpiWarps + kConvWarps;         // last warp: int8 weight producer
 constexpr int kTmemCols = 512;
+constexpr uint32_t kBytesW8 = kTileN * kBlockK;  // 8192
 
-constexpr uint32_t kBytesX = kMaxTileX * kBlockK * 2;  // 32768
-constexpr uint32_t kBytesA = kTileN * kBlockK * 2;     // 16384
-constexpr uint32_t kBytesW8 = kTileN * kBlockK;        // 8192
+// Where the widened weight tile (UMMA operand A) lives.
+//   kSmemA: converters write it to shared memory in the canonical K-major 128-byte-swizzled layout;
+//           activation tiles up to 256 rows, two 256-column accumulators fill tensor memory.
+//   kTmemA: converters write it straight into tensor memory (tcgen05.st) and the MMA reads A from
+//           there.  Shared memory then carries only the two TMA rings and one read of the int8 tile:
+//           80 KiB of shared-memory traffic per k-block instead of 112 KiB -- at full tensor rate the
+//           shared-memory path, not the tensor core, is what saturates.  Tensor memory holds two
+//           208-column accumulators plus three 32-column A stages, so activation tiles stop at 208 rows.
+enum AMode : int { kSmemA = 0, kTmemA = 1 };
 
-struct SmemLayout {
+template <int MODE>
+struct Cfg {
+    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : 208;  // activation rows per tile = UMMA N (multiple of 16)
+    static constexpr int kStagesX = MODE == kSmemA ? 4 : 6;       // activation tiles in flight
+    static constexpr int kStagesA = 3;                             // widened weight tiles (16 KiB shared / 32 columns)
+    static constexpr int kStagesW8 = MODE == kSmemA ? 4 : 6;      // int8 weight tiles (8 KiB each)
+    static constexpr int kAccStride = kMaxTileX;                   // columns between the two accumulators
+    static constexpr int kACol = 2 * kMaxTileX;                    // first tensor-memory column of the A stages (kTmemA)
+    static constexpr int kAColsPerStage = kBlockK / 2;             // two 16-bit k per 32-bit column
+    static constexpr uint32_t kBytesX = kMaxTileX * kBlockK * 2;  // 32768 / 26624, both multiples of 1024
+    static constexpr uint32_t kBytesA = MODE == kSmemA ? kTileN * kBlockK * 2 : 0;
+    // shared memory map
     static constexpr uint32_t x = 0;
     static constexpr uint32_t a = x + kStagesX * kBytesX;
     static constexpr uint32_t w8 = a + kStagesA * kBytesA;
     static constexpr uint32_t bars = w8 + kStagesW8 * kBytesW8;
-    // barriers: full_x[kStagesX], empty_x[kStagesX], full_w8, empty_w8, full_a, empty_a, tmem_full[2], tmem_empty[2]
+    // barriers: full_x, empty_x, full_w8, empty_w8, full_a, empty_a, tmem_full[2], tmem_empty[2]
     static constexpr uint32_t n_bars = 2 * kStagesX + 2 * kStagesW8 + 2 * kStagesA + 4;
     static constexpr uint32_t tmem_slot = bars + n_bars * 8;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
+    static constexpr uint32_t kSmemBytes = total + 1024;  // + slack to align the base to 1024 B
+    static_assert(kACol + kStagesA * kAColsPerStage <= kTmemCols || MODE == kSmemA, "tensor memory map");
+    static_assert(kSmemBytes <= 232448, "shared memory map");
 };
-constexpr uint32_t kSmemBytes = SmemLayout::total + 1024;  // + slack to align the base to 1024 B
 
 struct TcParams {
     int64_t M, N, K;
@@ -83,30 +120,130 @@ struct TcParams {
     int tiles_x;     // ceil(M / tile_x)
     int tiles_n;     // ceil(N / 128)
     unsigned int* error_flag;  // global; set to 1 when a bounded wait expired
+    // schedule (see work_item)
+    int full_rounds;  // rounds in which every CTA owns a whole tile
+    int rem_tiles;    // tiles of the last, partly filled round
+    int splits;       // K-splits per tile of that round (1 = whole tiles)
+    float* partial;   // [rem_tiles][splits][tile_x][128] fp32 partial products (splits > 1)
 };
+
+// One unit of work of a CTA: k-blocks [kb0, kb1) of an output tile.  split_slot >= 0 marks a
+// partial product that goes to slab split_slot of the workspace.
+struct WorkItem {
+    int tile, kb0, kb1, split_slot;
+};
+
+// idx-th item of this CTA; every warp role walks the same sequence.
+__device__ __forceinline__ bool work_item(const TcParams& p, int num_kb, int idx, WorkItem& w) {
+    const int P = (int)gridDim.x, b = (int)blockIdx.x;
+    if (idx < p.full_rounds) {
+        w.tile = b + idx * P; w.kb0 = 0; w.kb1 = num_kb; w.split_slot = -1;
+        return true;
+    }
+    if (idx > p.full_rounds || b >= p.rem_tiles * p.splits) return false;
+    const int j = b / p.splits, sp = b - j * p.splits;
+    w.tile = p.full_rounds * P + j;
+    w.kb0 = (int)((int64_t)sp * num_kb / p.splits);
+    w.kb1 = (int)((int64_t)(sp + 1) * num_kb / p.splits);
+    w.split_slot = p.splits > 1 ? b : -1;  // slab index = j * splits + sp
+    return true;
+}
 
 constexpr int kMaxKO = 64;  // outlier columns handled by the epilogue's CUDA-core side product
 
+#ifdef CB_TC_PROFILE
+// development only: per-CTA {start, end (globaltimer ns), SM id, items} of the last launch
+__device__ unsigned long long g_tc_prof[1024 * 4];
+__device__ __forceinline__ unsigned long long prof_now() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    return v;
+}
+#endif
+
+// Epilogue of one K-split of a tile (one warp = 32 output features x tile_x rows): store the fp32
+// partial accumulator to this split's slab, [row][feature] so that a warp writes 128 contiguous
+// bytes per row.  Kept out of line: the code of the ordinary epilogue is not affected by it.
+__device__ __noinline__ void epilogue_split(const TcParams& p, uint32_t taddr, int slab, int n_local, int64_t m_base) {
+    float* part = p.partial + (size_t)slab * ((size_t)p.tile_x * kTileN) + n_local;
+    for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            if (m_base + c0 + c >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
+            __stcg(part + (size_t)(c0 + c) * kTileN, __uint_as_float(r[c]));
+        }
+    }
+}
+
+// Second kernel of a call whose last round was split: one warp per output row of a split tile adds
+// the slabs in split order and finishes the row (scale, outlier side product, bias, one rounding).
 template <typename A>
+__global__ void __launch_bounds__(256) w8a16_tc_fixup_kernel(const __grid_constant__ TcParams p, int grid_main) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blocks_per_tile = (p.tile_x + 7) / 8;
+    const int j = blockIdx.x / blocks_per_tile;                      // tile of the split round
+    const int row = (blockIdx.x - j * blocks_per_tile) * 8 + warp;  // row inside the tile
+    const int tile = p.full_rounds * grid_main + j;
+    const int tx = tile % p.tiles_x, tn = tile / p.tiles_x;
+    const int64_t m = (int64_t)tx * p.tile_x + row;
+    if (row >= p.tile_x || m >= p.M) return;
+    const size_t slab_elems = (size_t)p.tile_x * kTileN;
+    const float* part = p.partial + (size_t)j * p.splits * slab_elems + (size_t)row * kTileN + lane;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int sp = 0; sp < p.splits; ++sp) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += __ldcg(part + sp * slab_elems + q * 32);
+    }
+    const A* xrow = static_cast<const A*>(p.xo) + m * p.ldxo;
+    A* y = static_cast<A*>(p.y);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int64_t n = (int64_t)tn * kTileN + q * 32 + lane;
+        if (n >= p.N) continue;
+        float v = acc[q] * load_scalar(p.scales, p.scales_dtype, n);
+        if (p.KO > 0) {
+            const A* wrow = static_cast<const A*>(p.wo) + n * p.KO;
+            for (int k = 0; k < (int)p.KO; ++k)
+                v = fmaf(Widen<A>::to_float(__ldg(xrow + k)), Widen<A>::to_float(__ldg(wrow + k)), v);
+        }
+        if (p.bias) v += load_scalar(p.bias, p.bias_dtype, n);
+        y[m * p.ldy + n] = Widen<A>::from_float(v);
+    }
+}
+
+template <typename A, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                const TcParams p) {
+                const __grid_constant__ TcParams p) {
+    using C = Cfg<MODE>;
+    constexpr int kStagesX = C::kStagesX, kStagesA = C::kStagesA, kStagesW8 = C::kStagesW8;
+    constexpr uint32_t kBytesX = C::kBytesX, kBytesA = C::kBytesA;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned base (the 128-byte swizzle pattern repeats every 1024 bytes)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t sx = base + SmemLayout::x, sa = base + SmemLayout::a, sw8 = base + SmemLayout::w8;
-    const uint32_t bars = base + SmemLayout::bars;
+    const uint32_t sx = base + C::x, sa = base + C::a, sw8 = base + C::w8;
+    const uint32_t bars = base + C::bars;
     const uint32_t full_x = bars, empty_x = full_x + 8 * kStagesX;
     const uint32_t full_w8 = empty_x + 8 * kStagesX, empty_w8 = full_w8 + 8 * kStagesW8;
     const uint32_t full_a = empty_w8 + 8 * kStagesW8, empty_a = full_a + 8 * kStagesA;
     const uint32_t tmem_full = empty_a + 8 * kStagesA, tmem_empty = tmem_full + 16;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + SmemLayout::tmem_slot);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + SmemLayout::abort_flag);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + C::tmem_slot);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + C::abort_flag);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (int)((p.K + kBlockK - 1) / kBlockK);
-    const int total_tiles = p.tiles_x * p.tiles_n;
+#ifdef CB_TC_PROFILE
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_tc_prof[blockIdx.x * 4 + 0] = prof_now();
+        g_tc_prof[blockIdx.x * 4 + 2] = smid;
+    }
+#endif
     const uint32_t x_bytes = (uint32_t)p.tile_x * kBlockK * 2;
 
     if (threadIdx.x == 0) {
@@ -119,7 +256,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         prefetch_tmap(&map_x);
         prefetch_tmap(&map_w);
     }
-    if (warp == 1) tmem_alloc(base + SmemLayout::tmem_slot, kTmemCols);
+    if (warp == 1) tmem_alloc(base + C::tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -133,9 +270,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int row_x = (t % p.tiles_x) * p.tile_x;
-                for (int kb = 0; kb < num_kb; ++kb) {
+            WorkItem w;
+            for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
+                const int row_x = (w.tile % p.tiles_x) * p.tile_x;
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(full_x + 8 * s, x_bytes);
@@ -150,13 +288,15 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             constexpr int kAhead = 12;  // k-blocks of weights requested into L2 ahead of their TMA load
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int row_w = (t / p.tiles_x) * kTileN;
-                const int row_w_next = ((t + (int)gridDim.x) / p.tiles_x) * kTileN;
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (kb + kAhead < num_kb) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kBlockK, row_w);
-                    else if (t + (int)gridDim.x < total_tiles)
-                        tma_prefetch_l2_2d(&map_w, (kb + kAhead - num_kb) * kBlockK, row_w_next);
+            WorkItem w, nx;
+            for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
+                const int row_w = (w.tile / p.tiles_x) * kTileN;
+                const bool has_next = work_item(p, num_kb, idx + 1, nx);
+                const int row_w_next = has_next ? (nx.tile / p.tiles_x) * kTileN : 0;
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                    if (kb + kAhead < w.kb1) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kBlockK, row_w);
+                    else if (has_next && nx.kb0 + (kb + kAhead - w.kb1) < nx.kb1)
+                        tma_prefetch_l2_2d(&map_w, (nx.kb0 + kb + kAhead - w.kb1) * kBlockK, row_w_next);
                     ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
@@ -174,13 +314,14 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             // latency overlaps the issue; this thread's loop is the critical path of the kernel.
             uint32_t s_a = 0, ph_a = 0, s_x = 0, ph_x = 0, it = 0;
             bool ok = true, pre = false;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+            WorkItem w;
+            for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx, ++it) {
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
                 ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!pre) {
                         const bool r0 = mbar_try(full_a + 8 * s_a, ph_a), r1 = mbar_try(full_x + 8 * s_x, ph_x);
                         ok = (r0 || mbar_wait(full_a + 8 * s_a, ph_a, abort_flag)) &&
@@ -192,13 +333,26 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     if (ns_a == kStagesA) { ns_a = 0; nph_a ^= 1u; }
                     if (ns_x == kStagesX) { ns_x = 0; nph_x ^= 1u; }
                     const bool n0 = mbar_try(full_a + 8 * ns_a, nph_a), n1 = mbar_try(full_x + 8 * ns_x, nph_x);
-                    const uint64_t adesc = make_kmajor_sw128_desc(sa + s_a * kBytesA);
                     const uint64_t bdesc = make_kmajor_sw128_desc(sx + s_x * kBytesX);
+#ifdef CB_TC_NOMMA  // development only
+                    if (p.M < 0)
+#endif
+                    if constexpr (MODE == kSmemA) {
+                        const uint64_t adesc = make_kmajor_sw128_desc(sa + s_a * kBytesA);
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 16; ++k) {
-                        // +32 bytes per 16-element k step: +2 in the (>>4) start-address field
-                        umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < kBlockK / 16; ++k) {
+                            // +32 bytes per 16-element k step: +2 in the (>>4) start-address field
+                            umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                                     (kb > w.kb0 || k > 0) ? 1u : 0u);
+                        }
+                    } else {
+                        const uint32_t a_tmem = tmem_base + C::kACol + s_a * C::kAColsPerStage;
+#pragma unroll
+                        for (int k = 0; k < kBlockK / 16; ++k) {
+                            // 16 k = 8 columns of A, 32 bytes of every B row
+                            umma_f16_tmem_a(d_tmem, a_tmem + (uint32_t)(8 * k), bdesc + (uint64_t)(2 * k), idesc,
+                                            (kb > w.kb0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(empty_a + 8 * s_a);  // both operand slots are free once these MMAs retire
                     umma_commit(empty_x + 8 * s_x);
@@ -217,10 +371,12 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         A* y = static_cast<A*>(p.y);
         uint32_t it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-            const int tx = t % p.tiles_x, tn = t / p.tiles_x;
+        WorkItem w;
+        for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx, ++it) {
+            const int tx = w.tile % p.tiles_x, tn = w.tile / p.tiles_x;
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
-            const int64_t n = (int64_t)tn * kTileN + quarter * 32 + lane;
+            const int n_local = quarter * 32 + lane;
+            const int64_t n = (int64_t)tn * kTileN + n_local;
             const bool n_ok = n < p.N;
             const float scale = n_ok ? load_scalar(p.scales, p.scales_dtype, n) : 0.0f;
             const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
@@ -232,9 +388,19 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const int64_t m_base = (int64_t)tx * p.tile_x;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccStride;
+            if (w.split_slot >= 0) {
+                // a K-split of a tile of the last round: rare path, kept out of line so that the code of
+                // the ordinary epilogue below is not affected by it
+                epilogue_split(p, taddr, w.split_slot, n_local, m_base);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+                continue;
+            }
             for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX + (uint32_t)c0, r);
+                tmem_ld32(taddr + (uint32_t)c0, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
@@ -259,11 +425,12 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
     } else if (warp < kW8Warp) {
         // ------------------------------ converters ------------------------------
-        const int cid = (warp - (2 + kEpiWarps)) * 32 + lane;  // 0 .. 255
+        const int cw = warp - (2 + kEpiWarps);  // 0 .. 7
         uint32_t s_w = 0, ph_w = 0, s_a = 0, ph_a = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            for (int kb = 0; kb < num_kb; ++kb) {
+        WorkItem w;
+        for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
+            for (int kb = w.kb0; kb < w.kb1; ++kb) {
                 {
                     // lane 0 probes both barriers back to back, the warp shares the verdict
                     int okw = 1;
@@ -276,32 +443,58 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t src = sw8 + s_w * kBytesW8, dst = sa + s_a * kBytesA;
+                const uint32_t src = sw8 + s_w * kBytesW8;
+                if constexpr (MODE == kSmemA) {
+                    const int cid = cw * 32 + lane;  // 0 .. 255
+                    const uint32_t dst = sa + s_a * kBytesA;
 #pragma unroll
-                for (int pass = 0; pass < (kTileN * kBlockK / 16) / (kConvWarps * 32); ++pass) {
-                    const int id = pass * (kConvWarps * 32) + cid;  // 16-byte chunk of the int8 tile
-                    const int row = id >> 2, j = id & 3;            // row of 64 codes, chunk j = k 16j .. 16j+15
-                    uint32_t c0, c1, c2, c3;
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-                                 : "r"(src + (uint32_t)(row * 64 + j * 16)));
-                    uint32_t o[8];
-                    Widen<A>::four(c0, o[0], o[1]);
-                    Widen<A>::four(c1, o[2], o[3]);
-                    Widen<A>::four(c2, o[4], o[5]);
-                    Widen<A>::four(c3, o[6], o[7]);
-                    // 16-bit row = 128 bytes = eight 16-byte chunks; chunk c lives at c ^ (row % 8)
-                    const uint32_t rbase = dst + (uint32_t)(row * 128);
-                    const uint32_t sw = (uint32_t)(row & 7);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rbase + (((uint32_t)(2 * j) ^ sw) << 4)),
-                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                 : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(rbase + (((uint32_t)(2 * j + 1) ^ sw) << 4)),
-                                 "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
-                                 : "memory");
+                    for (int pass = 0; pass < (kTileN * kBlockK / 16) / (kConvWarps * 32); ++pass) {
+                        const int id = pass * (kConvWarps * 32) + cid;  // 16-byte chunk of the int8 tile
+                        const int row = id >> 2, j = id & 3;            // row of 64 codes, chunk j = k 16j .. 16j+15
+                        uint32_t c0, c1, c2, c3;
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                                     : "r"(src + (uint32_t)(row * 64 + j * 16)));
+                        uint32_t o[8];
+                        CB_WIDEN<A>::four(c0, o[0], o[1]);
+                        CB_WIDEN<A>::four(c1, o[2], o[3]);
+                        CB_WIDEN<A>::four(c2, o[4], o[5]);
+                        CB_WIDEN<A>::four(c3, o[6], o[7]);
+                        // 16-bit row = 128 bytes = eight 16-byte chunks; chunk c lives at c ^ (row % 8)
+                        const uint32_t rbase = dst + (uint32_t)(row * 128);
+                        const uint32_t sw = (uint32_t)(row & 7);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rbase + (((uint32_t)(2 * j) ^ sw) << 4)),
+                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                     : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(rbase + (((uint32_t)(2 * j + 1) ^ sw) << 4)),
+                                     "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                                     : "memory");
+                    }
+                    fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
+                } else {
+                    // This thread owns weight row (32 * quarter + lane) = its tensor-memory lane and half of
+                    // the 64 k: warps 6..9 take k 0..31, warps 10..13 k 32..63.  The int8 tile arrived with
+                    // the 64-byte TMA swizzle (16-byte chunk c of row r sits at c ^ ((r >> 1) & 3)), so the
+                    // eight lanes of a quarter-warp hit eight different bank groups.
+                    const int quarter = warp & 3, khalf = cw >> 2;
+                    const int row = quarter * 32 + lane;
+                    const uint32_t rbase = src + (uint32_t)(row * 64);
+                    const uint32_t sw = (uint32_t)((row >> 1) & 3);
+                    uint32_t c[8];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(c[4 * j]), "=r"(c[4 * j + 1]), "=r"(c[4 * j + 2]), "=r"(c[4 * j + 3])
+                                     : "r"(rbase + ((((uint32_t)(2 * khalf + j)) ^ sw) << 4)));
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) CB_WIDEN<A>::four(c[j], o[2 * j], o[2 * j + 1]);
+                    tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                  (uint32_t)(C::kACol + s_a * C::kAColsPerStage + khalf * 16), o);
+                    tmem_st_wait();
+                    tc_fence_before();
                 }
-                fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(full_a + 8 * s_a);
@@ -321,6 +514,9 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         __syncwarp();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+#ifdef CB_TC_PROFILE
+    if (threadIdx.x == 0 && blockIdx.x < 1024) g_tc_prof[blockIdx.x * 4 + 1] = prof_now();
+#endif
     if (threadIdx.x == 0 && *abort_flag) {
         atomicExch(p.error_flag, 1u);
         __nanosleep(200000);  // let any TMA copy still in flight land before the CTA's memory is released
@@ -391,20 +587,92 @@ bool w8a16_tc_supported(const W8A16Args& a) {
     return encode_fn() != nullptr;
 }
 
-// Activation rows per tile: the multiple of 16 (<= 256) that wastes the fewest SM-slots over the
-// persistent schedule of ceil(M / tile) * ceil(N / 128) tiles on `sms` CTAs.
-static int pick_tile_x(int64_t M, int64_t N, int sms) {
-    const int64_t tiles_n = (N + kTileN - 1) / kTileN;
-    int best = 256;
-    double best_cost = 1e30;
-    for (int tx = 256; tx >= 32; tx -= 16) {
-        const int64_t tiles = ((M + tx - 1) / tx) * tiles_n;
-        const int64_t waves = (tiles + sms - 1) / sms;
-        // time ~ waves * (tile_x + fixed per-tile overhead expressed in rows)
-        const double cost = (double)waves * (tx + 512);  // measured: a k-block costs nearly the same for every tile height
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = tx; }
+// The persistent schedule of one call.
+struct TcPlan {
+    int mode;         // AMode
+    int tile_x;       // activation rows per tile (multiple of 16, <= 256 / 208)
+    int grid;         // CTAs
+    int full_rounds;  // rounds of whole tiles on every CTA
+    int rem_tiles;    // tiles of the last, partly filled round
+    int splits;       // K-splits of each of those (1 = none)
+    size_t partial_bytes;
+    size_t workspace_bytes() const { return partial_bytes; }
+};
+
+constexpr int kMaxSplits = 32;
+constexpr int kSplitOverheadKb = 24;  // slab stores + the second kernel, expressed in k-blocks (measured order of magnitude)
+
+static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, int sms, bool may_split, double* cost) {
+    TcPlan pl{};
+    const int64_t tiles = ((M + tx - 1) / tx) * ((N + kTileN - 1) / kTileN);
+    const int num_kb = (int)((K + kBlockK - 1) / kBlockK);
+    pl.mode = mode;
+    pl.tile_x = tx;
+    pl.full_rounds = (int)(tiles / sms);
+    pl.rem_tiles = (int)(tiles % sms);
+    pl.splits = 1;
+    // Split only a schedule that has no full round: there the idle SMs are a plain loss.  Behind full
+    // rounds the kernel is bound by what all SMs together pull out of L2, a thinly populated last round
+    // runs fast, and splitting it measured no gain (M = 1024 .. 4096, N = 14336, K = 4096).
+    if (may_split && pl.full_rounds == 0 && pl.rem_tiles > 0) {
+        int sp = sms / pl.rem_tiles;
+        if (sp > kMaxSplits) sp = kMaxSplits;
+        if (sp > num_kb / 2) sp = num_kb / 2;
+        // Worth it only with at least four splits per tile and a split round (its k-blocks + the slab
+        // traffic and the second kernel) clearly shorter than a whole tile; measured on B200: 32 tiles x 4
+        // splits is 23 % ahead at M = 128 and break-even at M = 256, 64 tiles x 2 splits is 14 % behind.
+        if (sp >= 4 && (num_kb + sp - 1) / sp + kSplitOverheadKb < (num_kb * 4) / 5) pl.splits = sp;
+    }
+    pl.grid = tiles >= sms || pl.splits > 1 ? sms : (int)tiles;
+    if (pl.splits > 1) pl.partial_bytes = (size_t)pl.rem_tiles * pl.splits * tx * kTileN * sizeof(float);
+    const double tail_kb = pl.rem_tiles == 0 ? 0.0
+                           : pl.splits > 1   ? (double)((num_kb + pl.splits - 1) / pl.splits + kSplitOverheadKb)
+                                             : (double)num_kb;
+    // time ~ k-blocks on the busiest CTA * (tile_x + a fixed per-k-block cost expressed in rows);
+    // measured: a k-block costs nearly the same for every tile height
+    *cost = ((double)pl.full_rounds * num_kb + tail_kb) * (tx + 512);
+    return pl;
+}
+
+// Operand-A mode and tile height (a multiple of 16 rows) with the shortest modelled schedule.
+// Mode: measured on B200 (N = 14336, K = 4096) the tensor-memory route is 7-10 % ahead while one
+// activation tile of <= 208 rows covers M, and behind from there on (its tiles are 208 rows, not 256).
+static TcPlan make_plan(int64_t M, int64_t N, int64_t K, int sms, bool may_split) {
+    int mode = M <= Cfg<kTmemA>::kMaxTileX ? kTmemA : kSmemA;
+#ifdef CB_TC_DEVTOOLS
+    if (const char* f = getenv("CB_TC_MODE")) mode = atoi(f) == kTmemA ? kTmemA : kSmemA;
+#endif
+    TcPlan best{};
+    double best_cost = 1e300;
+    for (int tx = (mode == kSmemA ? Cfg<kSmemA>::kMaxTileX : Cfg<kTmemA>::kMaxTileX); tx >= 32; tx -= 16) {
+        double cost;
+        const TcPlan pl = plan_for_tile(mode, tx, M, N, K, sms, may_split, &cost);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = pl; }
     }
     return best;
+}
+
+size_t w8a16_tc_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M < 1 || N < 1 || K < 1) return 0;
+    return make_plan(M, N, K, sm_count(), true).workspace_bytes();
+}
+
+template <typename A, int MODE>
+static cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, const TcParams& p, unsigned grid,
+                                  cudaStream_t s) {
+    using C = Cfg<MODE>;
+    // the opt-in shared-memory size is a per-device function attribute
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(w8a16_tc_kernel<A, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   C::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    w8a16_tc_kernel<A, MODE><<<grid, kThreads, C::kSmemBytes, s>>>(map_x, map_w, p);
+    return cudaPeekAtLastError();
 }
 
 cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
@@ -415,7 +683,16 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     p.bias = a.bias; p.bias_dtype = a.bias_dtype;
     p.xo = a.xo; p.wo = a.wo; p.KO = a.KO; p.ldxo = a.ldxo;
     p.y = a.y; p.ldy = a.ldy;
-    p.tile_x = pick_tile_x(a.M, a.N, sms);
+    TcPlan pl = make_plan(a.M, a.N, a.K, sms, true);
+    const bool ws_ok = a.workspace && a.workspace_bytes >= pl.workspace_bytes() &&
+                       (reinterpret_cast<uintptr_t>(a.workspace) & 15) == 0;
+    if (pl.splits > 1 && !ws_ok) pl = make_plan(a.M, a.N, a.K, sms, false);  // no workspace: whole tiles only
+#ifdef CB_TC_DEVTOOLS
+    if (getenv("CB_TC_NOSPLIT")) pl = make_plan(a.M, a.N, a.K, sms, false);
+#endif
+    p.tile_x = pl.tile_x;
+    p.full_rounds = pl.full_rounds; p.rem_tiles = pl.rem_tiles; p.splits = pl.splits;
+    p.partial = pl.splits > 1 ? static_cast<float*>(a.workspace) : nullptr;
     p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
     p.tiles_n = (int)((a.N + kTileN - 1) / kTileN);
     p.error_flag = error_word();
@@ -426,26 +703,22 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     if (!make_map_2d(&map_x, xdt, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx * 2, kBlockK, (uint32_t)p.tile_x,
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorNotSupported;
+    // the int8 tile is read by generic loads: plain rows for kSmemA, the 64-byte swizzle for kTmemA
     if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK,
-                     kTileN, CU_TENSOR_MAP_SWIZZLE_NONE))
+                     kTileN, pl.mode == kSmemA ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_64B))
         return cudaErrorNotSupported;
 
-    const int64_t tiles = (int64_t)p.tiles_x * p.tiles_n;
-    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    // the opt-in shared-memory size is a per-device function attribute
-    static bool attr_done[64][2] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int which = a.act_dtype == kBF16 ? 0 : 1;
-    if (dev >= 0 && dev < 64 && !attr_done[dev][which]) {
-        cudaError_t e = which == 0
-            ? cudaFuncSetAttribute(w8a16_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
-            : cudaFuncSetAttribute(w8a16_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_done[dev][which] = true;
-    }
-    if (which == 0) w8a16_tc_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, s>>>(map_x, map_w, p);
-    else w8a16_tc_kernel<__half><<<grid, kThreads, kSmemBytes, s>>>(map_x, map_w, p);
+    const unsigned grid = (unsigned)pl.grid;
+    const bool bf16 = a.act_dtype == kBF16;
+    cudaError_t e;
+    if (pl.mode == kSmemA) e = bf16 ? launch_variant<__nv_bfloat16, kSmemA>(map_x, map_w, p, grid, s)
+                                    : launch_variant<__half, kSmemA>(map_x, map_w, p, grid, s);
+    else e = bf16 ? launch_variant<__nv_bfloat16, kTmemA>(map_x, map_w, p, grid, s)
+                  : launch_variant<__half, kTmemA>(map_x, map_w, p, grid, s);
+    if (e != cudaSuccess || pl.splits <= 1) return e;
+    const unsigned fix_grid = (unsigned)(pl.rem_tiles * ((pl.tile_x + 7) / 8));
+    if (bf16) w8a16_tc_fixup_kernel<__nv_bfloat16><<<fix_grid, 256, 0, s>>>(p, pl.grid);
+    else w8a16_tc_fixup_kernel<__half><<<fix_grid, 256, 0, s>>>(p, pl.grid);
     return cudaPeekAtLastError();
 }
 
@@ -459,3 +732,10 @@ cudaError_t w8a16_tc_read_error(unsigned int* host_value, cudaStream_t s) {
 }
 
 }  // namespace cb
+
+#ifdef CB_TC_PROFILE
+extern "C" int cb_dev_tc_profile(unsigned long long* host, int ctas) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, cb::g_tc_prof, sizeof(unsigned long long) * 4 * ctas);
+}
+#endif

@@ -159,6 +159,7 @@ int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int6
  *   wo [N, KO] in act_dtype;  y [M, N].
  * Limit: M * (round_up(K - KO, 8) + round_up(KO, 8)) * 2 bytes <= cb_static_scratch_bytes(),
  *   otherwise CB_ERR_RANGE with an explanatory cb_static_last_error(); nothing is launched.
+ *   What the two buffers leave of the array is handed to the GEMM as its workspace.
  * The first call on a device resolves the array's address; issue it before any stream capture.
  * All calls on a device share the array: it keeps the last call's contents (each call writes
  * what it reads, nothing must be pre-zeroed) and calls that overlap on the GPU race on it.

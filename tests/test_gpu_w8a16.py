@@ -72,6 +72,35 @@ def test_small_shapes_both_paths(M, N, K, bias, dtype, path):
     _check(y, O.w8a16_forward(x, lay, b), f"path {path} vs reference rounding order")
 
 
+@pytest.mark.parametrize("M,N,K,KO", [(400, 1000, 4096, 8), (70, 512, 4096, 3), (128, 4096, 4096, 0), (64, 2048, 8192, 5)])
+def test_split_k_last_round(M, N, K, KO):
+    """Shapes whose last round of tiles fills only part of the GPU: the tensor-core kernel splits those
+    tiles along K, sums the fp32 partial products in the workspace and lets the last split finish them
+    (scale, outlier side product, bias, store).  Ragged M and N, outlier columns and a bias included."""
+    from cublade_b200 import _native as Nat
+    from cublade_b200.bindings.w8a16 import PATH_TENSOR_CORE_SINGLE as PATH_TC, w8a16_linear
+
+    assert Nat.lib().cb_w8a16_workspace_bytes(M, N, K) > 0, "shape chosen so that the split round is planned"
+    g = torch.Generator().manual_seed(M + N + K)
+    dtype = torch.bfloat16
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(N, generator=g).to(dtype)
+    lay = O.w8a16_quantize(w, dtype)
+    xo = wo = None
+    ref = O.w8a16_forward_fp64(x, lay, b)
+    if KO:
+        xo = (torch.randn(M, KO, generator=g) * 20).to(dtype)
+        wo = (torch.randn(N, KO, generator=g) * 0.05).to(dtype)
+        ref = ref + xo.double() @ wo.double().T
+    ys = [w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda(),
+                       x_outlier=xo.cuda() if KO else None, w_outlier=wo.cuda() if KO else None, path=PATH_TC)
+          for _ in range(2)]
+    _check(ys[0], ref, "split-K round")
+    _check(ys[1], ref, "split-K round, second call (workspace re-zeroed)")
+    assert Nat.device_error_state() == 0
+
+
 @pytest.mark.parametrize("M", [1, 16, 128])
 @pytest.mark.parametrize("n_out", [8, 3])
 def test_llm_int8_outlier_split(M, n_out):

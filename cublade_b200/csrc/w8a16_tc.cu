@@ -125,6 +125,9 @@ struct TcParams {
     int rem_tiles;    // tiles of the last, partly filled round
     int splits;       // K-splits per tile of that round (1 = whole tiles)
     float* partial;   // [rem_tiles][splits][tile_x][128] fp32 partial products (splits > 1)
+#ifdef CB_TC_DEVTOOLS
+    int dev_x_rows;   // development only: rows actually fetched per activation stage (0 = tile_x)
+#endif
 };
 
 // One unit of work of a CTA: k-blocks [kb0, kb1) of an output tile.  split_slot >= 0 marks a
@@ -244,7 +247,11 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         g_tc_prof[blockIdx.x * 4 + 2] = smid;
     }
 #endif
+#ifdef CB_TC_DEVTOOLS
+    const uint32_t x_bytes = (uint32_t)(p.dev_x_rows > 0 ? p.dev_x_rows : p.tile_x) * kBlockK * 2;
+#else
     const uint32_t x_bytes = (uint32_t)p.tile_x * kBlockK * 2;
+#endif
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStagesX; ++i) { mbar_init(full_x + 8 * i, 1); mbar_init(empty_x + 8 * i, 1); }
@@ -698,9 +705,14 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     p.error_flag = error_word();
     if (!p.error_flag) return cudaErrorUnknown;
 
+    uint32_t x_box_rows = (uint32_t)p.tile_x;
+#ifdef CB_TC_DEVTOOLS
+    p.dev_x_rows = getenv("CB_TC_XROWS") ? atoi(getenv("CB_TC_XROWS")) : 0;
+    if (p.dev_x_rows > 0) x_box_rows = (uint32_t)p.dev_x_rows;
+#endif
     CUtensorMap map_x, map_w;
     const CUtensorMapDataType xdt = a.act_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    if (!make_map_2d(&map_x, xdt, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx * 2, kBlockK, (uint32_t)p.tile_x,
+    if (!make_map_2d(&map_x, xdt, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx * 2, kBlockK, x_box_rows,
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorNotSupported;
     // the int8 tile is read by generic loads: plain rows for kSmemA, the 64-byte swizzle for kTmemA

@@ -255,6 +255,49 @@ class Int8GroupWorkload(Int8ChannelWorkload):
         return O.int8_dequantize_rows(q, s, torch.bfloat16)
 
 
+class RmsnormInt8Workload(Int8ChannelWorkload):
+    """Fused RMSNorm -> per-token INT8 quantize of bf16 activations [tokens, hidden], then dequantize."""
+
+    name = "rmsnorm_int8"
+    dominant = "rmsnorm_quant_rows_kernel (one-pass RMSNorm + per-token INT8 quantize)"
+
+    def __init__(self, device, rows=16384, cols=8192, sets=2):
+        from cublade_b200 import workloads as W
+
+        self.rows, self.cols, self.sets = rows, cols, sets
+        x_host = W.int8_group_case(rows, cols)  # Student-t activations, the same generator as the per-group config
+        self._host_buffers(x_host, device, sets)
+        g = torch.Generator().manual_seed(4)
+        self.gain_host = (1.0 + 0.1 * torch.randn(cols, generator=g)).to(torch.bfloat16)
+        self.gain = self.gain_host.to(device) if device is not None else None
+        self.n = rows * cols
+        self.q_bytes = self.n * 3 + rows * 4 + cols * 2  # x once in, codes once out, one scale per token, the gain
+        self.dq_bytes = self.n * 3 + rows * 4
+        self.bytes_per_step = self.q_bytes + self.dq_bytes
+        self.device = device
+        self.qt = [None] * sets
+        self.launches_per_step = 2
+        self.kernel_ms = []
+
+    def config(self):
+        c = super().config()
+        c["workload"] = (f"rmsnorm+int8_per_token_quant (fused, 3 B/elem instead of 7 unfused) + dequant bf16 "
+                         f"{self.rows}x{self.cols} (Student-t nu=3 x0.5)")
+        c["seed"] = 2
+        return c
+
+    def quantize(self, x):
+        from cublade_b200.quantization import rmsnorm_quantize_tensor
+
+        return rmsnorm_quantize_tensor(x, self.gain)
+
+    def cpu_step(self, x_cpu):
+        from oracle import oracle as O
+
+        q, s, _, _ = O.rmsnorm_quantize(x_cpu, self.gain_host)
+        return O.int8_dequantize_rows(q, s, torch.bfloat16)
+
+
 class Fp8ShardedWorkload(Int8ChannelWorkload):
     """Per-tensor FP8 E4M3 quantize + dequantize of ONE bf16 tensor of 2^33 elements, N(0,1), rows
     split contiguously over the ranks (strong scaling): local amax, one NCCL max-allreduce of a
@@ -332,6 +375,7 @@ class Fp8ShardedWorkload(Int8ChannelWorkload):
 
 
 WORKLOADS = {"int8_channel": Int8ChannelWorkload, "fp8_tensor": Fp8TensorWorkload, "int8_group": Int8GroupWorkload,
+             "rmsnorm_int8": RmsnormInt8Workload,
              "fp8_sharded": Fp8ShardedWorkload}
 
 

@@ -51,6 +51,13 @@ SIGNATURES = {
     "cb_w8a16_linear_outlier_static": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64,
                                                   c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int32, c_void_p,
                                                   c_void_p, c_int64, c_int32, c_void_p]),
+    "cb_w8a8_linear": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int32, c_void_p,
+                                 c_int32, c_void_p, c_int64, c_int32, c_void_p]),
+    "cb_quantize_per_axis_int8": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p,
+                                            c_void_p, c_void_p]),
+    "cb_dequantize_per_axis_int8": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p]),
+    "cb_rmsnorm_quantize": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_float, c_float, c_int32, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_gather_columns": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p]),
 }
 

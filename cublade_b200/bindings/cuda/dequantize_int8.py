@@ -46,3 +46,27 @@ def dequantize_per_group_int8(q_grouped: torch.Tensor, scale: torch.Tensor, grou
         N.check(N.lib().cb_dequantize_per_group_int8(q_grouped.data_ptr(), scale.data_ptr(), G, int(group_size),
                                                      N.dtype_code(dtype), y.data_ptr(), N.stream_ptr(q_grouped)))
     return y
+
+
+def dequantize_per_axis_int8(q: torch.Tensor, scale: torch.Tensor, axis: int,
+                             dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``y = dtype(float(q) * scale[index along axis])`` for any ``axis`` of a contiguous code tensor, in place
+    (the inverse of ``quantize_per_axis_int8``; the reference's dequantizer serves axis 0 only,
+    cublade/quantization/dequantizers.py:51-53)."""
+    check_dequant_input(q, scale, dtype, torch.int8, "torch.int8")
+    require(q.dim() >= 1, "q must have at least 1 dim")
+    require(-q.dim() <= axis < q.dim(), f"axis {axis} out of range for a {q.dim()}-d tensor")
+    axis %= q.dim()
+    C = q.size(axis)
+    require(scale.numel() == C and scale.is_contiguous(), "scale must be contiguous with one entry per index of axis")
+    outer = 1
+    for d in q.shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in q.shape[axis + 1:]:
+        inner *= d
+    with N.device_guard(q):
+        y = torch.empty(q.shape, dtype=dtype, device=q.device)
+        N.check(N.lib().cb_dequantize_per_axis_int8(q.data_ptr(), scale.data_ptr(), outer, C, inner, N.dtype_code(dtype),
+                                                    y.data_ptr(), N.stream_ptr(q)))
+    return y

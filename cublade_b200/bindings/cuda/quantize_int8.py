@@ -58,3 +58,29 @@ def quantize_per_group_int8(x_grouped: torch.Tensor, group_size: int, eps: float
                                                    int(group_size), float(eps), q.data_ptr(), scale.data_ptr(),
                                                    N.stream_ptr(x_grouped)))
     return q, scale
+
+
+def quantize_per_axis_int8(x: torch.Tensor, axis: int, eps: float = 1e-12) -> tuple[torch.Tensor, torch.Tensor]:
+    """One scale per index of ``axis`` (any axis) of a contiguous tensor, quantized in place without
+    moving the axis.  Beyond the reference, whose per-channel kernel serves axis 0 only
+    (cublade/quantization/quantizers.py:117-120); the result equals
+    ``quantize_per_channel_int8(x.movedim(axis, 0).contiguous())`` moved back, bit for bit.
+    Returns ``(q int8 like x, scale float32 [x.shape[axis]])``."""
+    check_quant_input(x, _ALLOWED, _TEXT)
+    require(x.dim() >= 1, "x must have at least 1 dim for per-channel quant")
+    require(-x.dim() <= axis < x.dim(), f"axis {axis} out of range for a {x.dim()}-d tensor")
+    axis %= x.dim()
+    C = x.size(axis)
+    outer = 1
+    for d in x.shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in x.shape[axis + 1:]:
+        inner *= d
+    with N.device_guard(x):
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        scale = torch.empty((C,), dtype=torch.float32, device=x.device)
+        scratch = torch.empty((max(C, 1),), dtype=torch.float32, device=x.device)
+        N.check(N.lib().cb_quantize_per_axis_int8(x.data_ptr(), N.dtype_code(x.dtype), outer, C, inner, float(eps),
+                                                  q.data_ptr(), scale.data_ptr(), scratch.data_ptr(), N.stream_ptr(x)))
+    return q, scale

@@ -209,4 +209,63 @@ int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int6
                        "cb_gather_columns", 1);
 }
 
+int32_t cb_w8a8_linear(const void* xq, const float* x_scales, int64_t M, int64_t K, const void* wq, int64_t N,
+                       const void* w_scales, int32_t w_scales_dtype, const void* bias, int32_t bias_dtype, void* y,
+                       int64_t ldy, int32_t out_dtype, void* stream) {
+    if (out_dtype != CB_F16 && out_dtype != CB_BF16)
+        return fail(CB_ERR_DTYPE, "cb_w8a8_linear: out_dtype must be float16 or bfloat16");
+    if (!is_float_like(w_scales_dtype) || (bias && !is_float_like(bias_dtype)))
+        return fail(CB_ERR_DTYPE, "cb_w8a8_linear: scales / bias must be float16, bfloat16 or float32");
+    if (M < 0 || N < 0 || K < 0) return fail(CB_ERR_ARGUMENT, "cb_w8a8_linear: negative size");
+    if (M == 0 || N == 0) return CB_OK;
+    if (K == 0) return fail(CB_ERR_ARGUMENT, "cb_w8a8_linear: K must be positive");
+    if (!xq || !x_scales || !wq || !w_scales || !y) return fail(CB_ERR_ARGUMENT, "cb_w8a8_linear: null pointer");
+    if (ldy < N) return fail(CB_ERR_ARGUMENT, "cb_w8a8_linear: ldy < N");
+    cb::W8A8Args a;
+    a.xq = static_cast<const int8_t*>(xq); a.xs = x_scales; a.M = M; a.K = K;
+    a.wq = static_cast<const int8_t*>(wq); a.N = N;
+    a.ws = w_scales; a.ws_dtype = w_scales_dtype; a.bias = bias; a.bias_dtype = bias_dtype;
+    a.y = y; a.ldy = ldy; a.out_dtype = out_dtype;
+    return cuda_result(cb::launch_w8a8(a, as_stream(stream)), "cb_w8a8_linear", 1);
+}
+
+int32_t cb_quantize_per_axis_int8(const void* x, int32_t dtype, int64_t outer, int64_t C, int64_t inner, float eps, void* q,
+                                  float* scale, float* scratch, void* stream) {
+    if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "cb_quantize_per_axis_int8: x must be float16, bfloat16 or float32");
+    if (outer < 0 || C < 0 || inner < 0) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_axis_int8: negative size");
+    if (C == 0) return CB_OK;
+    if (!scale || !scratch) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_axis_int8: null scale or scratch");
+    if (outer * inner > 0 && (!x || !q)) return fail(CB_ERR_ARGUMENT, "cb_quantize_per_axis_int8: null pointer");
+    const int launches = outer * inner > 0 ? 3 : 1;
+    return cuda_result(cb::launch_quant_axis(x, dtype, outer, C, inner, eps, q, scale, scratch, as_stream(stream)),
+                       "cb_quantize_per_axis_int8", launches);
+}
+
+int32_t cb_dequantize_per_axis_int8(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner,
+                                    int32_t out_dtype, void* y, void* stream) {
+    if (out_dtype != CB_F16 && out_dtype != CB_BF16)
+        return fail(CB_ERR_DTYPE, "cb_dequantize_per_axis_int8: out_dtype must be float16 or bfloat16");
+    if (outer < 0 || C < 0 || inner < 0) return fail(CB_ERR_ARGUMENT, "cb_dequantize_per_axis_int8: negative size");
+    if (outer * C * inner == 0) return CB_OK;
+    if (!q || !scale || !y) return fail(CB_ERR_ARGUMENT, "cb_dequantize_per_axis_int8: null pointer");
+    return cuda_result(cb::launch_dequant_axis(q, scale, outer, C, inner, out_dtype, y, as_stream(stream)),
+                       "cb_dequantize_per_axis_int8", 1);
+}
+
+int32_t cb_rmsnorm_quantize(const void* x, int32_t dtype, int64_t rows, int64_t hidden, const void* gamma, float rms_eps,
+                            float q_eps, int32_t code_kind, void* q, float* scale, void* y_out, float* rstd_out,
+                            void* stream) {
+    if (dtype != CB_F16 && dtype != CB_BF16)
+        return fail(CB_ERR_DTYPE, "cb_rmsnorm_quantize: x must be float16 or bfloat16");
+    if (code_kind != 0 && code_kind != 1) return fail(CB_ERR_ARGUMENT, "cb_rmsnorm_quantize: code_kind must be 0 (int8) or 1 (e4m3)");
+    if (rows < 0 || hidden < 0) return fail(CB_ERR_ARGUMENT, "cb_rmsnorm_quantize: negative size");
+    if (rows == 0 || hidden == 0) return CB_OK;
+    if (!x || !q || !scale) return fail(CB_ERR_ARGUMENT, "cb_rmsnorm_quantize: null pointer");
+    if (rows > 0x7fffffffLL) return fail(CB_ERR_RANGE, "cb_rmsnorm_quantize: more than 2^31 - 1 rows");
+    return cuda_result(cb::launch_rmsnorm_quant(x, dtype, rows, hidden, gamma, rms_eps, q_eps,
+                                                code_kind == 1 ? cb::kCodeE4M3 : cb::kCodeInt8, q, scale, y_out,
+                                                rstd_out, as_stream(stream)),
+                       "cb_rmsnorm_quantize", 1);
+}
+
 }  // extern "C"

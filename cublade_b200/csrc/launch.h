@@ -33,6 +33,20 @@ cudaError_t launch_amax_partials(const void* x, int dtype, int64_t n, float* par
 cudaError_t launch_quant_segments(const void* x, int dtype, int64_t nseg, int64_t L, float eps, int code, void* q,
                                   float* scale_out, cudaStream_t s);
 
+// ---- per-channel INT8 along any axis of a contiguous [outer, C, inner] tensor, in place (no transpose) ----
+// scratch: C floats, overwritten.  scale_out: C floats.
+cudaError_t launch_quant_axis(const void* x, int dtype, int64_t outer, int64_t C, int64_t inner, float eps, void* q,
+                              float* scale_out, float* scratch, cudaStream_t s);
+cudaError_t launch_dequant_axis(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner, int out_dtype,
+                                void* y, cudaStream_t s);
+
+// ---- fused RMSNorm -> per-row quantize ----------------------------------------
+// x [rows, H] fp16 / bf16; gamma [H] of the same type or nullptr; q [rows, H] codes; scale_out [rows];
+// y_out [rows, H] (the normalised rows in x's type) or nullptr; rstd_out [rows] (1 / rms) or nullptr.
+cudaError_t launch_rmsnorm_quant(const void* x, int dtype, int64_t rows, int64_t H, const void* gamma, float rms_eps,
+                                 float q_eps, int code, void* q, float* scale_out, void* y_out, float* rstd_out,
+                                 cudaStream_t s);
+
 // ---- dequantize -------------------------------------------------------------
 // seg_len == 0: one scale for the whole tensor; otherwise scale[i / seg_len].
 cudaError_t launch_dequant(const void* q, int code, const float* scale, int64_t n, int64_t seg_len, int out_dtype,
@@ -61,6 +75,23 @@ struct W8A16Args {
 size_t w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 // path: 0 = automatic, 1 = weight-streaming (skinny M) kernel, 2 = tcgen05 CTA-pair GEMM, 3 = tcgen05 single-CTA GEMM
 cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s);
+// ---- W8A8 linear ---------------------------------------------------------------
+struct W8A8Args {
+    const int8_t* xq;   // [M, K] int8 activations, row-major
+    const float* xs;    // [M] per-token scales
+    int64_t M, K;
+    const int8_t* wq;   // [N, K] int8 weights, row-major
+    int64_t N;
+    const void* ws;     // [N] per-output-channel scales
+    int ws_dtype;       // kF16 / kBF16 / kF32
+    const void* bias;   // [N] or nullptr
+    int bias_dtype;
+    void* y;            // [M, N] of out_dtype, row stride ldy
+    int64_t ldy;
+    int out_dtype;      // kBF16 or kF16
+};
+cudaError_t launch_w8a8(const W8A8Args& a, cudaStream_t s);
+
 // reads (and leaves untouched) the per-device flag a kernel raises when one of its bounded waits
 // expired; synchronises the stream.
 cudaError_t w8a16_tc_read_error(unsigned int* host_value, cudaStream_t s);

@@ -132,6 +132,16 @@ __device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a
         ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// integer MMA: A and B signed 8-bit (K = 32 per instruction), int32 accumulator
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // 32 lanes x 16 columns of 32 bits, registers -> tensor memory
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
@@ -178,6 +188,12 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
 __device__ __forceinline__ uint32_t make_idesc(bool bf16, uint32_t n) {
     const uint32_t fmt = bf16 ? 1u : 0u;
     return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((uint32_t)(kUmmaM >> 4) << 24);
+}
+
+// Instruction descriptor, kind::i8: int32 accumulate (format 2), A and B signed 8-bit (format 1), both
+// K-major, M = 128, N = tile_x.
+__device__ __forceinline__ uint32_t make_idesc_i8(uint32_t n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(kUmmaM >> 4) << 24);
 }
 
 template <typename A>

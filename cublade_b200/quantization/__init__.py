@@ -5,6 +5,8 @@ from .dequantizers import dequantize_tensor
 from .linear import cuBladeW8A16LinearLayer, cubladeW8A16LinearLayer
 from .quantizers import quantize_tensor, quantize_model
 from .outlier_utils import detect_outlier_columns, separate_outliers, split_weights_by_outliers
+from .fused import rmsnorm_quantize_tensor
+from .linear_w8a8 import cuBladeW8A8LinearLayer
 
 __all__ = [
     "quantize_model",
@@ -16,4 +18,6 @@ __all__ = [
     "detect_outlier_columns",
     "separate_outliers",
     "split_weights_by_outliers",
+    "rmsnorm_quantize_tensor",
+    "cuBladeW8A8LinearLayer",
 ]

@@ -6,6 +6,7 @@ import torch
 
 from ..bindings.cuda.dequantize_fp8 import dequantize_per_tensor_fp8 as _fp8_tensor
 from ..bindings.cuda.dequantize_int8 import (
+    dequantize_per_axis_int8 as _int8_axis,
     dequantize_per_channel_int8 as _int8_channel,
     dequantize_per_group_int8 as _int8_group,
     dequantize_per_tensor_int8 as _int8_tensor,
@@ -41,7 +42,8 @@ def dequantize_tensor(qt: QuantizedTensor) -> torch.Tensor:
             return _int8_tensor(qt.data, qt.scale, qt.original_dtype)
         if qt.mode == "channel":
             if qt.axis != 0:
-                raise NotImplementedError("INT8 channel dequant requires axis=0; got axis=" + str(qt.axis))
+                # beyond the reference (NotImplementedError at dequantizers.py:51-53): any axis, in place
+                return _int8_axis(qt.data, qt.scale, qt.axis, qt.original_dtype)
             return _int8_channel(qt.data, qt.scale, qt.original_dtype)
         if qt.mode == "group":
             if qt.group_size is None:

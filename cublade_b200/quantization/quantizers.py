@@ -12,6 +12,7 @@ import torch.nn as nn
 
 from ..bindings.cuda.quantize_fp8 import quantize_per_tensor_fp8 as _fp8_tensor
 from ..bindings.cuda.quantize_int8 import (
+    quantize_per_axis_int8 as _int8_axis,
     quantize_per_channel_int8 as _int8_channel,
     quantize_per_group_int8 as _int8_group,
     quantize_per_tensor_int8 as _int8_tensor,
@@ -73,8 +74,9 @@ def quantize_tensor(
 
     * ``scheme``: only ``"symmetric"`` (else ``NotImplementedError``).
     * ``dtype``: ``torch.int8`` (input fp16/bf16/fp32) or ``torch.float8_e4m3fn`` (input fp16/bf16, ``mode="tensor"`` only).
-    * ``mode``: ``"tensor"`` one scale; ``"channel"`` one scale per index of axis 0 (``ch_axis`` must be 0,
-      else ``NotImplementedError``); ``"group"`` one scale per ``group_size`` consecutive elements
+    * ``mode``: ``"tensor"`` one scale; ``"channel"`` one scale per index of ``ch_axis`` (the reference serves
+      axis 0 only and raises ``NotImplementedError`` otherwise; here any axis is quantized in place, with the
+      result of moving the axis to the front, quantizing and moving it back); ``"group"`` one scale per ``group_size`` consecutive elements
       along ``ch_axis`` (which is moved last first; ``group_size`` must divide it, else ``ValueError``).
       Group scales come back flat, ``(num_groups,)``, in the moved layout's order.
     * an unregistered ``(mode, dtype)`` pair, a CPU / non-contiguous tensor or a wrong input dtype raise ``ValueError``.
@@ -93,9 +95,14 @@ def quantize_tensor(
     if mode == "tensor":
         q, scale = kernel(x, eps)
     elif mode == "channel":
-        if ch_axis != 0:
-            raise NotImplementedError("INT8 channel quant requires ch_axis=0; got ch_axis=" + str(ch_axis))
-        q, scale = kernel(x, eps)
+        if ch_axis == 0:
+            q, scale = kernel(x, eps)
+        else:
+            # beyond the reference, which stops here with NotImplementedError (quantizers.py:117-120):
+            # any axis, quantized where it lies
+            if not -x.dim() <= ch_axis < x.dim():
+                raise ValueError(f"quantize_tensor: ch_axis {ch_axis} out of range for a {x.dim()}-d tensor")
+            q, scale = _int8_axis(x, ch_axis, eps)
     elif mode == "group":
         moved = x.movedim(ch_axis, -1).contiguous()
         lead, length = moved.shape[:-1], moved.shape[-1]
@@ -115,8 +122,10 @@ QUANT_LAYER_REGISTRY = {}
 def _init_registry():
     if not QUANT_LAYER_REGISTRY:
         from .linear import cuBladeW8A16LinearLayer
+        from .linear_w8a8 import cuBladeW8A8LinearLayer
 
         QUANT_LAYER_REGISTRY["w8a16"] = cuBladeW8A16LinearLayer
+        QUANT_LAYER_REGISTRY["w8a8"] = cuBladeW8A8LinearLayer  # reserved, not implemented, in the reference
 
 
 def quantize_model(

@@ -147,6 +147,55 @@ int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int6
                           int64_t ld_dst, int32_t elem_size, void* stream);
 
 /* ------------------------------------------------------------------------
+ * W8A8 linear on the integer tensor cores (tcgen05 kind::i8, exact int32 accumulation):
+ *   y[m, n] = T( (float(sum_k xq[m, k] * wq[n, k]) * x_scales[m]) * w_scales[n] + bias[n] )
+ * The layer type the reference reserves as "w8a8" (cublade/quantization/quantizers.py:169-171) and does
+ * not implement.  xq [M, K] int8 row-major with x_scales fp32[M] (per token -- e.g. the outputs of
+ * cb_quantize_per_channel_int8 on [M, K] or of cb_rmsnorm_quantize); wq [N, K] int8 row-major with
+ * w_scales [N]; bias [N] or NULL; y [M, N] CB_BF16 / CB_F16, rows ldy apart.  Products are evaluated
+ * in the order written, every operation a single IEEE fp32 operation, one rounding to T at the end.
+ * K % 16 == 0 with 16-byte aligned xq / wq runs on the tensor cores, anything else on a plain kernel.
+ * ------------------------------------------------------------------------ */
+int32_t cb_w8a8_linear(const void* xq, const float* x_scales, int64_t M, int64_t K, const void* wq, int64_t N,
+                       const void* w_scales, int32_t w_scales_dtype, const void* bias, int32_t bias_dtype, void* y,
+                       int64_t ldy, int32_t out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * INT8 per-channel along ANY axis, in place: x contiguous, viewed as [outer, C, inner] with C the
+ * channel axis.  Same arithmetic per channel as cb_quantize_per_channel_int8, so the result equals
+ * "move the axis to the front, quantize per channel, move it back" bit for bit -- without the copy.
+ * The reference advertises the mode (README.md:16) but rejects every axis but 0
+ *   cublade/quantization/quantizers.py:117-120, cublade/quantization/dequantizers.py:51-53
+ * scale: fp32[C].  scratch: C floats of device memory, overwritten.  Two passes over x
+ * (per-channel amax by atomicMax, then the cast); no alignment or divisibility requirement
+ * (vector kernels when inner % lanes == 0, or inner == 1 and C % lanes == 0, with 16-byte aligned x).
+ * ------------------------------------------------------------------------ */
+int32_t cb_quantize_per_axis_int8(const void* x, int32_t dtype, int64_t outer, int64_t C, int64_t inner, float eps, void* q,
+                                  float* scale, float* scratch, void* stream);
+int32_t cb_dequantize_per_axis_int8(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner,
+                                    int32_t out_dtype, void* y, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Fused RMSNorm -> per-row (per-token) quantize: one pass over x, 3 bytes of HBM traffic per
+ * element instead of the 7 of "RMSNorm kernel, then per-channel quantize kernel".
+ * The reference announces the op (README.md:20, "upcoming RMSNorm-fused-quant work" for which its
+ * DTypeTraits / Pack16 headers, cublade/kernels/cuda/quantization/int8_pack.cuh:23-100, are meant)
+ * but does not implement it; the second half is the arithmetic of
+ * cublade/kernels/cuda/quantization/quantize_int8.cu:173-297 (per-channel, axis 0).
+ *   x [rows, hidden] CB_F16 / CB_BF16, contiguous.  gamma [hidden] of the same dtype or NULL.
+ *   r = 1 / sqrt(mean(x^2) + rms_eps);  n = T(x * r);  y = T(n * gamma);
+ *   inv = qmax / max(max|y|, q_eps);  q = code(float(y) * inv);  scale[row] = 1 / inv
+ *   code_kind 0: int8 (qmax 127, codes in [-127, 127]); 1: e4m3 (qmax 448).
+ *   q [rows, hidden] bytes; scale fp32[rows]; y_out [rows, hidden] in x's dtype receives y, or NULL;
+ *   rstd_out fp32[rows] receives r, or NULL.
+ * Any hidden and alignment are served; rows of hidden % 8 == 0, hidden <= 16384 with 16-byte
+ * aligned pointers take the register-resident one-pass kernel.
+ * ------------------------------------------------------------------------ */
+int32_t cb_rmsnorm_quantize(const void* x, int32_t dtype, int64_t rows, int64_t hidden, const void* gamma, float rms_eps,
+                            float q_eps, int32_t code_kind, void* q, float* scale, void* y_out, float* rstd_out,
+                            void* stream);
+
+/* ------------------------------------------------------------------------
  * LLM.int8 W8A16 linear for callers that cannot allocate device memory.
  * No counterpart in the reference (which allocates freely through torch).
  *

@@ -95,6 +95,21 @@ def int8_quantize_channel(x: torch.Tensor, eps: float = 1e-12):
     return q.reshape(x.shape), s
 
 
+def int8_quantize_axis(x: torch.Tensor, axis: int, eps: float = 1e-12):
+    """Per channel along any axis: the axis-0 quantizer (quantize_int8.cu:487-509) applied to the tensor with
+    ``axis`` moved to the front, codes moved back.  Returns (q like x, scale [x.shape[axis]])."""
+    moved = x.detach().to("cpu").movedim(axis, 0).contiguous()
+    q, s = int8_quantize_channel(moved, eps)
+    return q.movedim(0, axis).contiguous(), s
+
+
+def int8_dequantize_axis(q: torch.Tensor, scale: torch.Tensor, axis: int, out_dtype: torch.dtype = torch.bfloat16):
+    """y = T_rn(float(q) * scale[index along axis]) (dequantize_int8.cu:81-108 with the axis in place)."""
+    shape = [1] * q.dim()
+    shape[axis] = -1
+    return (q.detach().to("cpu").float() * scale.detach().to("cpu").float().view(shape)).to(out_dtype)
+
+
 def int8_quantize_group(x_grouped: torch.Tensor, group_size: int, eps: float = 1e-12):
     """Per group on a [num_groups, group_size] view: (q same, scale [num_groups]).  quantize_int8.cu:514-536."""
     assert x_grouped.dim() == 2 and x_grouped.shape[1] == group_size
@@ -105,6 +120,43 @@ def int8_dequantize_rows(q2d: torch.Tensor, scale: torch.Tensor, out_dtype: torc
     """cublade/kernels/cuda/quantization/dequantize_int8.cu:39-63, :81-108, :129-133: y = T_rn(float(q) * s_row)."""
     s = scale.detach().to("cpu").float().reshape(-1, 1)
     return (q2d.detach().to("cpu").float() * s).to(out_dtype)
+
+
+# ---------------------------------------------------------------------------------------
+# RMSNorm -> per-row quantize (the fused op the reference announces in README.md:20; the second
+# half is int8_quantize_rows / the FP8 cast above applied per row)
+# ---------------------------------------------------------------------------------------
+def rmsnorm_rows(x2d: torch.Tensor, gamma: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
+                 rstd: Optional[torch.Tensor] = None):
+    """RMSNorm of the rows of ``x2d [R, H]`` (fp16 / bf16) with the roundings of an unfused layer:
+    ``n = T(x * r)``, ``y = T(float(n) * float(gamma))``.  ``r = 1 / sqrt(mean(x^2) + rms_eps)`` in float32
+    from a float64 sum of squares (the exact value a float32 summation approximates), unless ``rstd``
+    supplies it.  Returns (y in x's dtype, r float32 [R])."""
+    x32 = x2d.detach().to("cpu").float()
+    if rstd is None:
+        mean = (x32.double().pow(2).sum(dim=1) / x32.shape[1]).float()
+        r = (1.0 / torch.sqrt((mean + _f32(rms_eps)).double())).float()
+    else:
+        r = rstd.detach().to("cpu").float()
+    y = (x32 * r[:, None]).to(x2d.dtype)
+    if gamma is not None:
+        y = (y.float() * gamma.detach().to("cpu").float()[None, :]).to(x2d.dtype)
+    return y, r
+
+
+def rmsnorm_quantize(x2d: torch.Tensor, gamma: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
+                     code: torch.dtype = torch.int8, eps: float = 1e-12, rstd: Optional[torch.Tensor] = None):
+    """RMSNorm rows, then quantize every row on its own.  Returns (q, scale [R], y, r)."""
+    y, r = rmsnorm_rows(x2d, gamma, rms_eps, rstd)
+    if code == torch.int8:
+        q, s = int8_quantize_rows(y, eps)
+    else:
+        y32 = y.float()
+        a = torch.maximum(y32.abs().amax(dim=1), _f32(eps))
+        inv = _f32(E4M3_MAX) / a
+        q = (y32 * inv[:, None]).to(torch.float8_e4m3fn)
+        s = _f32(1.0) / inv
+    return q, s, y, r
 
 
 # ---------------------------------------------------------------------------------------
@@ -193,6 +245,25 @@ def w8a16_forward(x: torch.Tensor, layer: dict, bias: Optional[torch.Tensor] = N
     if bias is not None:
         y = y + bias.to(T)
     return y.reshape(*x.shape[:-1], q.shape[0])
+
+
+def w8a8_forward(x: torch.Tensor, layer: dict, bias: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, xq: Optional[torch.Tensor] = None,
+                 xs: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """W8A8 linear: per-token INT8 quantization of x (int8_quantize_rows on the [tokens, in] view, i.e.
+    quantize_int8.cu:487-509 with axis 0 = token), exact integer dot products, then
+    ``T((float(acc) * x_scale[m]) * w_scale[n] + bias[n])`` -- each step one float32 operation.
+    ``layer`` as returned by ``w8a16_quantize`` (int8 weights [N, K], scales in the layer dtype)."""
+    x2d = x.detach().to("cpu").reshape(-1, x.shape[-1])
+    if xq is None:
+        xq, xs = int8_quantize_rows(x2d)
+    acc = (xq.detach().to("cpu").double() @ layer["int8_weights"].double().t()).to(torch.int32)  # exact: |acc| < 2^53
+    y = acc.float() * xs.detach().to("cpu").float()[:, None]
+    y = y * layer["scales"].float()[None, :]
+    if bias is not None:
+        y = y + bias.detach().to("cpu").float()[None, :]
+    y = y.to(out_dtype or x.dtype)
+    return y.reshape(*x.shape[:-1], layer["int8_weights"].shape[0])
 
 
 def w8a16_forward_fp64(x: torch.Tensor, layer: dict, bias: Optional[torch.Tensor] = None) -> torch.Tensor:

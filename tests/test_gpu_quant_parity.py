@@ -242,8 +242,8 @@ def test_native_error_codes_and_python_exceptions():
         cb.quantize_tensor(x.float(), dtype=torch.float8_e4m3fn)  # fp32 not accepted for FP8
     with pytest.raises(ValueError):
         cb.quantize_tensor(x, dtype=torch.float8_e4m3fn, mode="channel")
-    with pytest.raises(NotImplementedError):
-        cb.quantize_tensor(x, dtype=torch.int8, mode="channel", ch_axis=1)
+    with pytest.raises(ValueError):  # (any in-range axis is served; the reference raises NotImplementedError for != 0)
+        cb.quantize_tensor(x, dtype=torch.int8, mode="channel", ch_axis=x.dim())
     with pytest.raises(NotImplementedError):
         cb.quantize_tensor(x, "asymmetric")
     with pytest.raises(ValueError, match="evenly divide"):

@@ -118,7 +118,7 @@ def test_replace_linear_layers_selection_and_bias_handling():
 def test_quantize_model_registry_errors_and_copy_semantics(monkeypatch):
     from cublade_b200.quantization import quantizers
 
-    with pytest.raises(ValueError, match="Unknown quant_type 'w4a16'. Available: w8a16"):
+    with pytest.raises(ValueError, match="Unknown quant_type 'w4a16'. Available: w8a16, w8a8"):
         cb.quantize_model(nn.Linear(4, 4), "w4a16")
     monkeypatch.setitem(quantizers.QUANT_LAYER_REGISTRY, "w8a16", _Recorder)
     model = nn.Sequential(nn.Linear(4, 4))
@@ -137,3 +137,28 @@ def test_w8a16_layer_buffers_and_state_dict_layout():
     assert cb.cuBladeW8A16LinearLayer(32, 16, bias=False).bias is None
     with pytest.raises(ValueError, match="CUDA"):
         layer(torch.zeros(2, 32, dtype=torch.bfloat16))
+
+
+def test_rmsnorm_quantize_oracle_known_answers_and_cpu_rejection():
+    """Hand-checked rows for the CPU formulation of the fused RMSNorm -> quantize op, and the wrapper's
+    refusal of CPU tensors (there is no CPU path)."""
+    import pytest
+    import torch
+
+    from oracle import oracle as O
+    from cublade_b200.quantization import rmsnorm_quantize_tensor
+
+    x = torch.tensor([[3.0, 4.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0]], dtype=torch.bfloat16)  # mean(x^2) = 25/8
+    q, s, y, r = O.rmsnorm_quantize(x, None, rms_eps=0.0)
+    assert abs(r.item() - (8.0 / 25.0) ** 0.5) < 1e-7
+    assert y.tolist() == [[torch.tensor(3.0 * r.item()).to(torch.bfloat16).item(),
+                           torch.tensor(4.0 * r.item()).to(torch.bfloat16).item(), 0, 0, 0, 0, 0, 0]]
+    assert q.tolist()[0][:2] == [95, 127] and q.tolist()[0][2:] == [0] * 6  # 3/4 * 127 = 95.25
+    gain = torch.tensor([2.0, 0.5, 1, 1, 1, 1, 1, 1], dtype=torch.bfloat16)
+    q2, s2, y2, _ = O.rmsnorm_quantize(x, gain, rms_eps=0.0)
+    assert y2[0, 0].item() == 2 * y[0, 0].item() and y2[0, 1].item() == 0.5 * y[0, 1].item()
+    assert q2.tolist()[0][:2] == [127, 42]  # (4/2) / (3*2) * 127 = 42.33
+    qf, sf, _, _ = O.rmsnorm_quantize(x, None, rms_eps=0.0, code=torch.float8_e4m3fn)
+    assert qf.float().tolist()[0][:2] == [320.0, 448.0]  # 336 ties to the even neighbour 320
+    with pytest.raises(ValueError):
+        rmsnorm_quantize_tensor(x)

@@ -438,25 +438,28 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)  # launchers such as torchrun pin OMP_NUM_THREADS=1
-    if args.workload == "w8a16":
+    if args.workload in ("w8a16", "w8a8"):
         from cublade_b200 import workloads as W
         from oracle import oracle as O
 
+        a8 = args.workload == "w8a8"
+        forward = O.w8a8_forward if a8 else O.w8a16_forward
         M = min(args.m, 64)
         w, x, _ = W.w8a16_case(M)
         lay = O.w8a16_quantize(w, torch.bfloat16)
-        O.w8a16_forward(x, lay)
+        forward(x, lay)
         steps = max(1, min(args.steps, 5))
         t0 = time.perf_counter()
         for _ in range(steps):
-            O.w8a16_forward(x, lay)
+            forward(x, lay)
         dt = (time.perf_counter() - t0) / steps
         v = 2.0 * M * 14336 * 4096 / dt / 1e12
         sample = f"first {M} of {args.m} activation rows per step (reference CPU branch of the layer), {steps} steps"
-        print(json.dumps({"impl": "reference", "metric": "W8A16 TFLOPS", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        metric = "W8A8 TOPS (2*M*N*K per step, activation quantization included)" if a8 else "W8A16 TFLOPS"
+        print(json.dumps({"impl": "reference", "metric": metric, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
                           "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": f"w8a16_linear M={args.m} N=14336 K=4096"},
+                          "scaling": "strong", "vs_baseline": None, "dtype": "int8" if a8 else "bf16", "data": "synthetic",
+                          "config": {"workload": f"{args.workload}_linear M={args.m} N=14336 K=4096"},
                           "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                                            "sample": sample},
                           "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
@@ -499,7 +502,9 @@ def run_w8a16(args, rank, world, local_rank, device, dist):
     M, N_, K_ = args.m, 14336, 4096
     w, x_host, _ = W.w8a16_case(M)
     n0, n1 = shard_range(N_, rank, world)
-    layer = cb.cuBladeW8A16LinearLayer(K_, n1 - n0, bias=False, dtype=torch.bfloat16)
+    a8 = args.workload == "w8a8"  # int8 activations (quantized per token inside the step) on the integer tensor cores
+    layer_cls = cb.quantization.cuBladeW8A8LinearLayer if a8 else cb.cuBladeW8A16LinearLayer
+    layer = layer_cls(K_, n1 - n0, bias=False, dtype=torch.bfloat16)
     layer.quantize(w[n0:n1].to(device))
     layer = layer.to(device)
     x_pinned = x_host.pin_memory()
@@ -561,21 +566,39 @@ def run_w8a16(args, rank, world, local_rank, device, dist):
             if tensor_bound else
             {"bound": "hbm", "achieved": bytes_local / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
              "frac": bytes_local / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
-    roof.update({"kernel": "w8a16_tc_kernel (tcgen05/TMEM)" if M >= 65 else "w8a16_stream_kernel", "traffic": None,
+    roof.update({"kernel": "w8a16_tc_kernel (tcgen05/TMEM)" if M >= 17 else "w8a16_stream_kernel", "traffic": None,
                  "peak_source": peaks["source"], "avg_launch_us": ms * 1e3})
-    out = {"metric": "W8A16 TFLOPS", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": warmup,
-           "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-           "data": "synthetic",
-           "config": {"workload": f"w8a16_linear M={M} N={N_} K={K_} int8 per-output-channel weights, bf16 activations",
+    if a8:
+        roof["kernel"] = "w8a8_tc_kernel (tcgen05 kind::i8) + per-token quantize_segments_kernel"
+        roof["peak_note"] = ("measured cuBLAS bf16 figure; no int8 peak was measured on this pool, the integer path's "
+                             "nominal rate is twice the bf16 one")
+    out = {"metric": "W8A8 TOPS (2*M*N*K per step, activation quantization included)" if a8 else "W8A16 TFLOPS", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": warmup,
+           "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "int8" if a8 else "bf16", "data": "synthetic",
+           "config": {"workload": f"{args.workload}_linear M={M} N={N_} K={K_} int8 per-output-channel weights, bf16 activations"
+                                  + (" quantized per token to int8 in the step" if a8 else ""),
                       "l2_policy": "back-to-back replays; weights (58.7 MB) + activations stay L2-resident, the shape is "
                                    "tensor-bound" if tensor_bound else "back-to-back replays (L2-resident weights)",
                       "launch": "one CUDA graph per step", "seed": 3, "sharding": f"output features over {world} rank(s)"},
            "clocks": clocks.summary(),
            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K_ * 2,
                    "d2h_bytes_per_step": M * (n1 - n0) * 2, "ms_per_step": e2e_ms, "steps": steps_e2e},
-           "gpu_launches": K, "gpu_launches_note": "1 kernel of libcublade_b200.so per step, replayed from a CUDA graph",
+           "gpu_launches": K * (2 if a8 else 1),
+           "gpu_launches_note": f"{2 if a8 else 1} kernel(s) of libcublade_b200.so per step, replayed from a CUDA graph",
            "roofline": roof}
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and a8:
+        from oracle import oracle as O
+
+        torch.set_num_threads(os.cpu_count() or 1)
+        ms_cpu = min(M, 64)
+        lay = O.w8a16_quantize(w, torch.bfloat16)
+        O.w8a8_forward(x_host[:ms_cpu], lay)
+        t0 = time.perf_counter()
+        O.w8a8_forward(x_host[:ms_cpu], lay)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": 2.0 * ms_cpu * N_ * K_ / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                               "kind": "port", "sample": f"first {ms_cpu} activation rows, one forward after one warm-up"}
+    elif not args.no_cpu_baseline:
         # the reference's own CPU branch of the layer (x @ W.t() in the activation dtype), bounded sample
         from oracle import oracle as O
 
@@ -619,7 +642,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS) + ["w8a16"])
+    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS) + ["w8a16", "w8a8"])
     ap.add_argument("--m", type=int, default=2048, help="activation rows for --workload w8a16")
     ap.add_argument("--impl", default="cublade_b200", choices=["cublade_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -647,7 +670,7 @@ def main():
     from cublade_b200 import _native as N
 
     N.lib()  # fail loudly if the extension is missing
-    if args.workload == "w8a16":
+    if args.workload in ("w8a16", "w8a8"):
         run_w8a16(args, rank, world, local_rank, device, dist)
         if dist is not None:
             dist.barrier()

@@ -64,7 +64,7 @@ def test_quantize_tensor_routes_other_axes_and_round_trips():
     assert_bits_equal(y, O.int8_dequantize_axis(q_ref, s_ref, 1, torch.bfloat16), "dequant")
     # per-column scales keep every column within half a step; one scale per row could not
     err = (y.cpu().float() - x.float()).abs()
-    assert (err <= 0.5 * s_ref[None, :] * 1.01 + 1e-30).all()
+    assert (err <= 0.5 * s_ref[None, :] * 1.01 + x.float().abs() * 2.0 ** -8 + 1e-30).all()  # + bf16 rounding of y
 
 
 def test_full_size_last_axis_equals_transposed_axis0_path_on_the_gpu():

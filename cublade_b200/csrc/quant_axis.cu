@@ -33,6 +33,13 @@ __device__ __forceinline__ void atomic_max_abs(float* slot, float m) {
     if (m > 0.0f) atomicMax(reinterpret_cast<unsigned int*>(slot), __float_as_uint(m));
 }
 
+// channel of pack p when a channel run is ppr packs long: (p / ppr) % C.  64-bit division is an
+// instruction sequence of its own; tensors below 2^31 packs (every real one) take the 32-bit route.
+__device__ __forceinline__ int64_t channel_of_pack(int64_t p, int64_t ppr, int64_t C, bool small) {
+    if (small) return (int64_t)(((uint32_t)p / (uint32_t)ppr) % (uint32_t)C);
+    return (p / ppr) % C;
+}
+
 template <typename T>
 __device__ __forceinline__ float pack_absmax(const uint4& raw) {
     AbsMax<T> am;
@@ -49,8 +56,13 @@ __global__ void __launch_bounds__(kBlock) amax_runs_kernel(const T* __restrict__
     const uint4* xp = reinterpret_cast<const uint4*>(x);
     constexpr int kChunkPacks = kBlock * 4;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
+    const bool small = npk < 0x7fffffffLL && C < 0x7fffffffLL;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float red[kBlock / 32];
     for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-        const int64_t p0 = c * kChunkPacks + threadIdx.x;
+        const int64_t first = c * kChunkPacks;
+        const int64_t last = first + kChunkPacks - 1 < npk ? first + kChunkPacks - 1 : npk - 1;
+        const int64_t p0 = first + threadIdx.x;
         uint4 v[4];
         bool ok[4];
 #pragma unroll
@@ -58,18 +70,36 @@ __global__ void __launch_bounds__(kBlock) amax_runs_kernel(const T* __restrict__
             ok[k] = p0 + k * kBlock < npk;
             v[k] = ok[k] ? ld_keep16(xp + p0 + k * kBlock) : make_uint4(0u, 0u, 0u, 0u);
         }
+        const int64_t run_first = small ? (int64_t)((uint32_t)first / (uint32_t)ppr) : first / ppr;
+        const int64_t run_last = small ? (int64_t)((uint32_t)last / (uint32_t)ppr) : last / ppr;
+        if (run_first == run_last) {
+            // the whole 16 KiB chunk lies in one channel run: one atomic for the CTA
+            AbsMax<T> am;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int64_t p = p0 + k * kBlock;
-            const int64_t ch = ok[k] ? (p / ppr) % C : -1;
-            float m = pack_absmax<T>(v[k]);
-            // a warp reads 32 adjacent packs: when they all lie in one channel, one atomic serves the warp
-            const int64_t ch0 = __shfl_sync(0xffffffffu, ch, 0);
-            if (__all_sync(0xffffffffu, ch == ch0)) {
-                m = team_max<32>(m);
-                if ((threadIdx.x & 31) == 0 && ch0 >= 0) atomic_max_abs(amax + ch0, m);
-            } else if (ch >= 0) {
-                atomic_max_abs(amax + ch, m);
+            for (int k = 0; k < 4; ++k) am.update(v[k]);
+            float m = team_max<32>(am.finish());
+            if (lane == 0) red[warp] = m;
+            __syncthreads();
+            if (warp == 0) {
+                m = team_max<8>(lane < kBlock / 32 ? red[lane] : 0.0f);
+                if (lane == 0) atomic_max_abs(amax + (small ? (int64_t)((uint32_t)run_first % (uint32_t)C) : run_first % C), m);
+            }
+            __syncthreads();
+        } else {
+            // runs shorter than a chunk: lanes of a warp that share a channel elect one of them
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int64_t p = p0 + k * kBlock;
+                const int ch = ok[k] ? (int)channel_of_pack(p, ppr, C, small) : -1;
+                const unsigned bits = __float_as_uint(pack_absmax<T>(v[k]));
+                if (small) {
+                    const unsigned peers = __match_any_sync(0xffffffffu, ch);
+                    const unsigned top = __reduce_max_sync(peers, bits);
+                    if (ch >= 0 && lane == __ffs(peers) - 1 && top != 0u)
+                        atomicMax(reinterpret_cast<unsigned int*>(amax) + ch, top);
+                } else if (ok[k]) {
+                    atomic_max_abs(amax + channel_of_pack(p, ppr, C, false), __uint_as_float(bits));
+                }
             }
         }
     }
@@ -82,6 +112,7 @@ __global__ void __launch_bounds__(kBlock) cast_runs_kernel(const T* __restrict__
     const uint4* xp = reinterpret_cast<const uint4*>(x);
     constexpr int kChunkPacks = kBlock * 4;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
+    const bool small = npk < 0x7fffffffLL && C < 0x7fffffffLL;
     for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const int64_t p0 = c * kChunkPacks + threadIdx.x;
         uint4 v[4];
@@ -93,7 +124,7 @@ __global__ void __launch_bounds__(kBlock) cast_runs_kernel(const T* __restrict__
             ok[k] = p < npk;
             if (ok[k]) {
                 v[k] = ld_stream16(xp + p);
-                iv[k] = __ldg(inv + (p / ppr) % C);
+                iv[k] = __ldg(inv + channel_of_pack(p, ppr, C, small));
             }
         }
 #pragma unroll
@@ -123,12 +154,12 @@ __global__ void __launch_bounds__(kBlock) amax_last_kernel(const T* __restrict__
 #pragma unroll
     for (int e = 0; e < E; ++e) m[e] = 0.0f;
     int64_t r = r0;
-    for (; r + 4 <= r1; r += 4) {  // four rows in flight
-        uint4 v[4];
+    for (; r + 8 <= r1; r += 8) {  // eight rows in flight
+        uint4 v[8];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = ld_keep16(xp + (r + k) * cpk);
+        for (int k = 0; k < 8; ++k) v[k] = ld_keep16(xp + (r + k) * cpk);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 8; ++k) {
             float f[E];
             pack_to_floats<T>(v[k], f);
 #pragma unroll
@@ -172,12 +203,12 @@ __global__ void __launch_bounds__(kBlock) cast_last_kernel(const T* __restrict__
         }
     };
     int64_t r = r0;
-    for (; r + 4 <= r1; r += 4) {
-        uint4 v[4];
+    for (; r + 8 <= r1; r += 8) {
+        uint4 v[8];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = ld_stream16(xp + (r + k) * cpk);
+        for (int k = 0; k < 8; ++k) v[k] = ld_stream16(xp + (r + k) * cpk);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) emit(r + k, v[k]);
+        for (int k = 0; k < 8; ++k) emit(r + k, v[k]);
     }
     for (; r < r1; ++r) emit(r, ld_stream16(xp + r * cpk));
 }
@@ -226,12 +257,14 @@ __global__ void __launch_bounds__(kBlock) dequant_axis_kernel(const uint8_t* __r
         const int64_t ppr = LAYOUT == 0 ? inner / 8 : 0, cpk = LAYOUT == 1 ? C / 8 : 0;
         const uint2* qp = reinterpret_cast<const uint2*>(q);
         uint4* yp = reinterpret_cast<uint4*>(y);
+        const bool small = npk < 0x7fffffffLL && C < 0x7fffffffLL;
         for (int64_t p = (int64_t)blockIdx.x * kBlock + threadIdx.x; p < npk; p += (int64_t)gridDim.x * kBlock) {
             const uint2 codes = ld_stream8(qp + p);
             if constexpr (LAYOUT == 0) {
-                st_stream16(yp + p, codes_decode8<OutT, Int8Code>(codes, __ldg(scale + (p / ppr) % C)));
+                st_stream16(yp + p, codes_decode8<OutT, Int8Code>(codes, __ldg(scale + channel_of_pack(p, ppr, C, small))));
             } else {
-                const float4* sp = reinterpret_cast<const float4*>(scale) + (p % cpk) * 2;
+                const int64_t cp = small ? (int64_t)((uint32_t)p % (uint32_t)cpk) : p % cpk;
+                const float4* sp = reinterpret_cast<const float4*>(scale) + cp * 2;
                 const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
                 float a[4], b[4];
                 Int8Code::decode4(codes.x, a);
@@ -275,9 +308,10 @@ cudaError_t quant_axis_t(const void* xv, int64_t outer, int64_t C, int64_t inner
     } else if (n > 0 && al && inner == 1 && C % E == 0) {
         const int64_t cpk = C / E, rows = outer;
         const unsigned gx = (unsigned)((cpk + kBlock - 1) / kBlock);
-        // enough row slabs to fill the GPU eight CTAs deep, at least 16 rows each
-        int64_t slabs = ((int64_t)sm_count() * 8 + gx - 1) / gx;
-        if (slabs > (rows + 15) / 16) slabs = (rows + 15) / 16;
+        // enough row slabs to fill the GPU four CTAs deep (8 x 16 bytes in flight per thread), at least 32 rows
+        // each: every slab ends with one atomicMax per channel, so fewer, taller slabs mean less contention
+        int64_t slabs = ((int64_t)sm_count() * 4 + gx - 1) / gx;
+        if (slabs > (rows + 31) / 32) slabs = (rows + 31) / 32;
         if (slabs < 1) slabs = 1;
         if (slabs > 65535) slabs = 65535;
         const int64_t rows_per_slab = (rows + slabs - 1) / slabs;

@@ -46,6 +46,25 @@ __device__ __forceinline__ float block_reduce(float v, float* red) {
     return r;
 }
 
+// the same for N values at once (one pair of barriers for all of them); `red` holds N x 8 floats
+template <bool IS_MAX, int N>
+__device__ __forceinline__ void block_reduce_n(float (&v)[N], float (*red)[kBlock / 32]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        v[i] = IS_MAX ? team_max<32>(v[i]) : team_sum<32>(v[i]);
+        if (lane == 0) red[i][warp] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        float r = lane < kBlock / 32 ? red[i][lane] : 0.0f;
+        r = IS_MAX ? team_max<8>(r) : team_sum<8>(r);
+        v[i] = __shfl_sync(0xffffffffu, r, 0);
+    }
+    __syncthreads();
+}
+
 __device__ __forceinline__ float inv_rms(float ss, int64_t H, float rms_eps) {
     return __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), rms_eps));
 }
@@ -61,80 +80,115 @@ __device__ __forceinline__ float pack_sumsq(const uint4& raw) {
     return s;
 }
 
+// two lanes times two lanes in T: the product of two 16-bit floats is exact in fp32 (at most 22 significant
+// bits), so the packed multiply's single rounding equals "widen, multiply in fp32, round to T"
+__device__ __forceinline__ uint32_t mul2(__half, uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t mul2(__nv_bfloat16, uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // normalise one pack in place: y = T(T(x * r) * g)
 template <typename T, bool HAS_G>
 __device__ __forceinline__ uint4 pack_normalise(const uint4& raw, float r, const uint4& graw) {
-    float f[8], g[8];
+    float f[8];
     pack_to_floats<T>(raw, f);
-    if constexpr (HAS_G) pack_to_floats<T>(graw, g);
+    const uint32_t g[4] = {graw.x, graw.y, graw.z, graw.w};
     uint32_t w[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         w[k] = DTypeTraits<T>::float2_to_word(__fmul_rn(f[2 * k], r), __fmul_rn(f[2 * k + 1], r));
-        if constexpr (HAS_G) {
-            const float2 n = DTypeTraits<T>::word_to_float2(w[k]);
-            w[k] = DTypeTraits<T>::float2_to_word(__fmul_rn(n.x, g[2 * k]), __fmul_rn(n.y, g[2 * k + 1]));
-        }
+        if constexpr (HAS_G) w[k] = mul2(T(), w[k], g[k]);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// A TEAM of threads (32 lanes of a warp, or a whole 256-thread CTA) owns one row; thread t holds
-// packs t, t + TEAM, ... (PACKS of them) in registers.  Needs H % 8 == 0 and 16-byte aligned rows.
-template <typename T, typename Code, int TEAM, int PACKS, bool HAS_G>
-__global__ void __launch_bounds__(kBlock) rmsnorm_quant_rows_kernel(const T* __restrict__ x, int64_t rows, int npk,
+// A TEAM of threads (32 lanes of a warp, or a whole 256-thread CTA) owns ROWS rows at a time; thread t holds
+// packs t, t + TEAM, ... (PACKS of them) of each row in registers.  Needs H % 8 == 0 and 16-byte aligned rows.
+// ROWS = 2 halves the number of CTA barriers per row (the two rows' sums and maxima travel through the
+// same reductions) and loads the gain once for both.
+template <typename T, typename Code, int TEAM, int PACKS, int ROWS, bool HAS_G>
+__global__ void __launch_bounds__(kBlock, ROWS * PACKS <= 2 ? 6 : (ROWS * PACKS <= 4 ? 5 : 2)) rmsnorm_quant_rows_kernel(const T* __restrict__ x, int64_t rows, int npk,
                                                                     const T* __restrict__ gamma, float rms_eps,
                                                                     float q_eps, uint8_t* __restrict__ q,
                                                                     float* __restrict__ scale_out,
                                                                     T* __restrict__ y_out, float* __restrict__ rstd_out) {
     constexpr int kTeamsPerCta = kBlock / TEAM;
     const int t = threadIdx.x % TEAM;
-    const int64_t row = (int64_t)blockIdx.x * kTeamsPerCta + threadIdx.x / TEAM;
-    const bool live = row < rows;
-    const uint4* xp = reinterpret_cast<const uint4*>(x) + row * (int64_t)npk;
+    const int64_t row0 = ((int64_t)blockIdx.x * kTeamsPerCta + threadIdx.x / TEAM) * ROWS;
     const uint4* gp = reinterpret_cast<const uint4*>(gamma);
-    __shared__ float red[kBlock / 32];
+    __shared__ float red[ROWS][kBlock / 32];
 
-    uint4 v[PACKS];
-    float ss = 0.0f;
+    uint4 v[ROWS][PACKS];
 #pragma unroll
-    for (int k = 0; k < PACKS; ++k) {
-        const int p = t + k * TEAM;
-        if (live && p < npk) v[k] = ld_stream16(xp + p);
-        else v[k] = make_uint4(0u, 0u, 0u, 0u);
+    for (int r = 0; r < ROWS; ++r) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x) + (row0 + r) * (int64_t)npk;
+#pragma unroll
+        for (int k = 0; k < PACKS; ++k) {
+            const int p = t + k * TEAM;
+            v[r][k] = (row0 + r < rows && p < npk) ? ld_stream16(xp + p) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    float ss[ROWS], r_inv[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        ss[r] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < PACKS; ++k) ss[r] += pack_sumsq<T>(v[r][k]);
+    }
+    if constexpr (TEAM <= 32) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) ss[r] = team_sum<TEAM>(ss[r]);
+    } else {
+        block_reduce_n<false, ROWS>(ss, red);
     }
 #pragma unroll
-    for (int k = 0; k < PACKS; ++k) ss += pack_sumsq<T>(v[k]);
-    if constexpr (TEAM <= 32) ss = team_sum<TEAM>(ss);
-    else ss = block_reduce<false>(ss, red);
-    const float r = inv_rms(ss, (int64_t)npk * 8, rms_eps);
-    if (rstd_out && live && t == 0) rstd_out[row] = r;
+    for (int r = 0; r < ROWS; ++r) {
+        r_inv[r] = inv_rms(ss[r], (int64_t)npk * 8, rms_eps);
+        if (rstd_out && row0 + r < rows && t == 0) rstd_out[row0 + r] = r_inv[r];
+    }
 
-    AbsMax<T> am;
+    float m[ROWS];
+    AbsMax<T> am[ROWS];
 #pragma unroll
     for (int k = 0; k < PACKS; ++k) {
         const int p = t + k * TEAM;
         uint4 g = make_uint4(0u, 0u, 0u, 0u);
         if constexpr (HAS_G) {
-            if (p < npk) g = ld_keep16(gp + p);
+            if (p < npk) g = ld_keep16(gp + p);  // the gain: 2 * H bytes shared by every row, served by L1 / L2
         }
-        v[k] = pack_normalise<T, HAS_G>(v[k], r, g);  // packs beyond the row stay zero
-        am.update(v[k]);
-    }
-    float m = am.finish();
-    if constexpr (TEAM <= 32) m = team_max<TEAM>(m);
-    else m = block_reduce<true>(m, red);
-    const InvScale is = inv_and_scale<Code>(m, q_eps);
-    if (live && t == 0) scale_out[row] = is.scale;
-
-    uint8_t* qp = q + row * (int64_t)npk * 8;
-    uint4* yp = y_out ? reinterpret_cast<uint4*>(y_out) + row * (int64_t)npk : nullptr;
 #pragma unroll
-    for (int k = 0; k < PACKS; ++k) {
-        const int p = t + k * TEAM;
-        if (live && p < npk) {
-            st_stream8(qp + (int64_t)p * 8, pack_encode<T, Code>(v[k], is.inv));
-            if (yp) st_stream16(yp + p, v[k]);
+        for (int r = 0; r < ROWS; ++r) {
+            v[r][k] = pack_normalise<T, HAS_G>(v[r][k], r_inv[r], g);  // packs beyond the row stay zero
+            am[r].update(v[r][k]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) m[r] = am[r].finish();
+    if constexpr (TEAM <= 32) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) m[r] = team_max<TEAM>(m[r]);
+    } else {
+        block_reduce_n<true, ROWS>(m, red);
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int64_t row = row0 + r;
+        if (row >= rows) continue;
+        const InvScale is = inv_and_scale<Code>(m[r], q_eps);
+        if (t == 0) scale_out[row] = is.scale;
+        uint8_t* qp = q + row * (int64_t)npk * 8;
+        uint4* yp = y_out ? reinterpret_cast<uint4*>(y_out) + row * (int64_t)npk : nullptr;
+#pragma unroll
+        for (int k = 0; k < PACKS; ++k) {
+            const int p = t + k * TEAM;
+            if (p < npk) {
+                st_stream8(qp + (int64_t)p * 8, pack_encode<T, Code>(v[r][k], is.inv));
+                if (yp) st_stream16(yp + p, v[r][k]);
+            }
         }
     }
 }
@@ -180,11 +234,14 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 template <typename T, typename Code, int TEAM, int PACKS>
 void launch_rows(const T* x, int64_t rows, int npk, const T* gamma, float rms_eps, float q_eps, uint8_t* q,
                  float* scale_out, T* y_out, float* rstd_out, cudaStream_t s) {
-    constexpr int kTeamsPerCta = kBlock / TEAM;
-    const unsigned grid = (unsigned)((rows + kTeamsPerCta - 1) / kTeamsPerCta);
-    if (gamma) rmsnorm_quant_rows_kernel<T, Code, TEAM, PACKS, true><<<grid, kBlock, 0, s>>>(
+    // measured on B200 (16384 x 8192 bf16): two rows per team (half the barriers per row) is no faster than
+    // one and costs registers; what matters is occupancy -- 96 registers held the kernel to 2 CTAs per SM
+    constexpr int ROWS = 1;
+    constexpr int kRowsPerCta = kBlock / TEAM * ROWS;
+    const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
+    if (gamma) rmsnorm_quant_rows_kernel<T, Code, TEAM, PACKS, ROWS, true><<<grid, kBlock, 0, s>>>(
         x, rows, npk, gamma, rms_eps, q_eps, q, scale_out, y_out, rstd_out);
-    else rmsnorm_quant_rows_kernel<T, Code, TEAM, PACKS, false><<<grid, kBlock, 0, s>>>(
+    else rmsnorm_quant_rows_kernel<T, Code, TEAM, PACKS, ROWS, false><<<grid, kBlock, 0, s>>>(
         x, rows, npk, gamma, rms_eps, q_eps, q, scale_out, y_out, rstd_out);
 }
 

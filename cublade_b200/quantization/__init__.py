@@ -7,6 +7,7 @@ from .quantizers import quantize_tensor, quantize_model
 from .outlier_utils import detect_outlier_columns, separate_outliers, split_weights_by_outliers
 from .fused import rmsnorm_quantize_tensor
 from .linear_w8a8 import cuBladeW8A8LinearLayer
+from .checkpoint import load_quantized_model, load_quantized_state_dict, save_quantized_model
 
 __all__ = [
     "quantize_model",
@@ -20,4 +21,7 @@ __all__ = [
     "split_weights_by_outliers",
     "rmsnorm_quantize_tensor",
     "cuBladeW8A8LinearLayer",
+    "save_quantized_model",
+    "load_quantized_model",
+    "load_quantized_state_dict",
 ]

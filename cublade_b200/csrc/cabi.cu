@@ -209,6 +209,28 @@ int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int6
                        "cb_gather_columns", 1);
 }
 
+size_t cb_gemm_workspace_bytes(int64_t N, int64_t K, int32_t in_kind) {
+    if (N <= 0 || K <= 0 || in_kind < 0 || in_kind > 3) return 0;
+    return cb::tc_gemm_workspace_bytes(N, K, in_kind);
+}
+
+int32_t cb_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int32_t in_kind, void* c, int64_t ldc,
+                int32_t out_kind, void* workspace, size_t workspace_bytes, void* stream) {
+    if (in_kind < 0 || in_kind > 3) return fail(CB_ERR_DTYPE, "cb_gemm: in_kind must be 0 (fp16), 1 (bf16), 2 (int8) or 3 (uint8)");
+    const bool integer = in_kind >= 2;
+    if (integer ? out_kind != 2 : !(out_kind == 0 || (out_kind == 1 && in_kind == 0)))
+        return fail(CB_ERR_DTYPE, "cb_gemm: accumulator type does not go with the input type "
+                                  "(fp16 -> fp32 or fp16, bf16 -> fp32, int8 / uint8 -> int32)");
+    if (M < 0 || N < 0 || K < 0) return fail(CB_ERR_ARGUMENT, "cb_gemm: negative size");
+    if (M == 0 || N == 0) return CB_OK;
+    if (K == 0) return fail(CB_ERR_ARGUMENT, "cb_gemm: K must be positive");
+    if (!a || !b || !c) return fail(CB_ERR_ARGUMENT, "cb_gemm: null pointer");
+    if (ldc < N) return fail(CB_ERR_ARGUMENT, "cb_gemm: ldc < N");
+    return cuda_result(cb::launch_tc_gemm(a, b, M, N, K, in_kind, c, ldc, out_kind, workspace, workspace_bytes,
+                                          as_stream(stream)),
+                       "cb_gemm", 2);
+}
+
 int32_t cb_w8a8_linear(const void* xq, const float* x_scales, int64_t M, int64_t K, const void* wq, int64_t N,
                        const void* w_scales, int32_t w_scales_dtype, const void* bias, int32_t bias_dtype, void* y,
                        int64_t ldy, int32_t out_dtype, void* stream) {

@@ -147,6 +147,21 @@ int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int6
                           int64_t ld_dst, int32_t elem_size, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Dense GEMM  C[M, N] = A[M, K] . B[K, N], all row-major, on tcgen05 / TMEM.
+ * replaces wmma_gemm(A, B, acc_dtype)
+ *   cublade/kernels/cuda/wmma.cu:184-262 (kernel :29-182; binding cublade/bindings/cuda/wmma.py:16-47)
+ * in_kind: 0 fp16, 1 bf16, 2 int8, 3 uint8 (A and B of the same type).
+ * out_kind (type of C): 0 fp32 (fp16 / bf16 inputs), 1 fp16 (fp16 inputs; fp32 accumulation, one rounding),
+ *   2 int32 (8-bit inputs, exact).  Other pairings -> CB_ERR_DTYPE, as the reference rejects them.
+ * Unlike the reference M, N, K need not be multiples of 16.  workspace: cb_gemm_workspace_bytes(N, K,
+ * in_kind) bytes (B is transposed into it once per call); without it, or when K * sizeof(element) is not
+ * a multiple of 16, a plain CUDA-core kernel computes the product.
+ * ------------------------------------------------------------------------ */
+size_t cb_gemm_workspace_bytes(int64_t N, int64_t K, int32_t in_kind);
+int32_t cb_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int32_t in_kind, void* c, int64_t ldc,
+                int32_t out_kind, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * W8A8 linear on the integer tensor cores (tcgen05 kind::i8, exact int32 accumulation):
  *   y[m, n] = T( (float(sum_k xq[m, k] * wq[n, k]) * x_scales[m]) * w_scales[n] + bias[n] )
  * The layer type the reference reserves as "w8a8" (cublade/quantization/quantizers.py:169-171) and does

@@ -203,7 +203,7 @@ def test_checkpoint_round_trip_reproduces_the_forward_bit_for_bit(tmp_path):
         torch.manual_seed(3)
         m = nn.Sequential(nn.Linear(256, 512), nn.GELU(), nn.Linear(512, 128)).to(torch.bfloat16)
         with torch.no_grad():
-            m[0].weight[:, [3, 77, 200]] *= 40.0
+            m[0].weight[:, [3, 77, 200]] *= 400.0
         return m
 
     x = torch.randn(24, 256, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).cuda()

@@ -30,7 +30,7 @@ constexpr int kTileN = 128;       // columns of C per tile = UMMA M
 constexpr int kMaxTileX = 256;    // rows of C per tile = UMMA N
 constexpr int kRowBytes = 128;    // bytes of k per row and stage (one swizzle row)
 constexpr int kStages = 4;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;  // two per tensor-memory lane quarter, each draining every other 32-column chunk
 constexpr int kThreads = (3 + kEpiWarps) * 32;
 constexpr int kWWarp = 2 + kEpiWarps;
 constexpr int kTmemCols = 512;
@@ -170,20 +170,37 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             if (!ok) break;
             tc_fence_after();
+            // This warp takes every other chunk of 32 rows of C; the tcgen05.ld of its next chunk is in flight while
+            // the current one is stored (a load takes a few thousand cycles while the MMAs of the next tile run).
             const int64_t m_base = (int64_t)tx * p.tile_x;
-            for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX + (uint32_t)c0, r);
-                tmem_ld_wait();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX;
+            const int nchunks = (p.tile_x + 31) / 32, parts = kEpiWarps / 4;
+            auto store_chunk = [&](const uint32_t (&r)[32], int ch) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const int64_t m = m_base + c0 + c;
-                    if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
+                    const int64_t m = m_base + ch * 32 + c;
+                    if (m >= p.M || ch * 32 + c >= p.tile_x) break;  // uniform across the warp
                     if (!n_ok) continue;
                     // fp32 and int32 accumulators are stored as they are (the same 32 bits)
                     if (p.out_kind == kOutF16) static_cast<__half*>(p.c)[m * p.ldc + n] = __float2half_rn(__uint_as_float(r[c]));
                     else static_cast<uint32_t*>(p.c)[m * p.ldc + n] = r[c];
                 }
+            };
+            uint32_t ra[32], rb[32];
+            int ch = (warp - 2) >> 2;
+            if (ch < nchunks) tmem_ld32(taddr + (uint32_t)(ch * 32), ra);
+            while (ch < nchunks) {
+                tmem_ld_wait();
+                int nx = ch + parts;
+                if (nx < nchunks) tmem_ld32(taddr + (uint32_t)(nx * 32), rb);
+                store_chunk(ra, ch);
+                ch = nx;
+                if (ch >= nchunks) break;
+                tmem_ld_wait();
+                nx = ch + parts;
+                if (nx < nchunks) tmem_ld32(taddr + (uint32_t)(nx * 32), ra);
+                store_chunk(rb, ch);
+                ch = nx;
             }
             tc_fence_before();
             __syncwarp();

@@ -15,12 +15,13 @@
 // tensor-memory lanes), the ACTIVATION tile operand B (N = tile_x <= 256 rows = columns), so scale
 // and bias of an output feature are one scalar per epilogue thread.
 //
-// Warps of a CTA (one CTA per SM, persistent over output tiles): 0 TMA activations, 6 TMA weights,
-// 1 MMA issuer (+ tensor-memory allocation), 2-5 epilogue (overlaps the next tile: two accumulators).
+// Warps of a CTA (one CTA per SM, persistent over output tiles): 0 TMA activations, 10 TMA weights,
+// 1 MMA issuer (+ tensor-memory allocation), 2-9 epilogue (overlaps the next tile: two accumulators).
 // No TMA multicast, no clusters.  Every mbarrier wait is bounded; on expiry the kernel raises the
 // per-device error flag, all roles leave their loops, tensor memory is released, the kernel returns.
 #include "tc_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace cb {
@@ -35,7 +36,7 @@ constexpr int kTileN = 128;     // output features per tile = UMMA M
 constexpr int kMaxTileX = 256;  // activation rows per tile = UMMA N
 constexpr int kBlockK8 = 128;   // int8 k per stage: one 128-byte swizzle row
 constexpr int kStages = 4;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;  // two per tensor-memory lane quarter, each draining every other 32-column chunk
 constexpr int kThreads = (3 + kEpiWarps) * 32;
 constexpr int kWWarp = 2 + kEpiWarps;
 constexpr int kTmemCols = 512;
@@ -66,6 +67,69 @@ struct Params {
     int tile_x, tiles_x, tiles_n;
     unsigned int* error_flag;
 };
+
+// Epilogue of one tile for one warp: lanes = 32 output features (one tensor-memory lane quarter), `part` of
+// `parts` warps sharing the quarter takes every parts-th chunk of 32 token columns.  The tcgen05.ld of the
+// next chunk is in flight while the current one is scaled and stored: a tensor-memory load takes a few
+// thousand cycles while the MMAs of the next tile are writing the other accumulator, and a drain that
+// waits for each load on its own (first version) took 1.7x as long as the tile's main loop.
+template <typename T>
+__device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t taddr, int part, int parts, int64_t m_base,
+                                                  int64_t n, bool n_ok, float wscale, float bias, int lane) {
+    T* y = static_cast<T*>(p.y);
+    const int nchunks = (p.tile_x + 31) / 32;
+    auto scales_of = [&](int ch) {
+        const int64_t m_lane = m_base + ch * 32 + lane;
+        return m_lane < p.M ? __ldg(p.xs + m_lane) : 0.0f;  // one per-token scale per lane, handed round by shuffles
+    };
+    auto finish = [&](const uint32_t (&r)[32], int ch, float xs_lane) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const float xs = __shfl_sync(0xffffffffu, xs_lane, c);
+            const int64_t m = m_base + ch * 32 + c;
+            if (m >= p.M || ch * 32 + c >= p.tile_x) continue;  // uniform across the warp
+            float v = __fmul_rn(__fmul_rn(__int2float_rn((int)r[c]), xs), wscale);
+            if (p.bias) v = __fadd_rn(v, bias);
+            if (n_ok) y[m * p.ldy + n] = Widen<T>::from_float(v);
+        }
+    };
+    uint32_t ra[32], rb[32];
+    int ch = part;
+    if (ch < nchunks) tmem_ld32(taddr + (uint32_t)(ch * 32), ra);
+    while (ch < nchunks) {
+        float xs_lane = scales_of(ch);
+        tmem_ld_wait();
+        int nx = ch + parts;
+        if (nx < nchunks) tmem_ld32(taddr + (uint32_t)(nx * 32), rb);
+        finish(ra, ch, xs_lane);
+        ch = nx;
+        if (ch >= nchunks) break;
+        xs_lane = scales_of(ch);
+        tmem_ld_wait();
+        nx = ch + parts;
+        if (nx < nchunks) tmem_ld32(taddr + (uint32_t)(nx * 32), ra);
+        finish(rb, ch, xs_lane);
+        ch = nx;
+    }
+}
+
+#ifdef CB_TC_PROFILE
+// development only: cycle counters of CTA 0 -- [0] x producer waiting for a free stage, [1] w producer waiting,
+// [2] MMA thread waiting for a full stage, [3] MMA thread issuing + committing, [4] MMA thread waiting for the
+// accumulator, [5] k-blocks, [6] total cycles of the MMA thread, [7] epilogue warp 2 waiting for tmem_full,
+// [8] epilogue warp 2 draining
+__device__ unsigned long long g_w8a8_prof[16];
+// counters live in registers of the measuring thread and are written once when its role ends
+#define W8_PROF_DECL unsigned long long prof_acc[4] = {0, 0, 0, 0};
+#define W8_PROF_T0 const long long prof_t0 = clock64();
+#define W8_PROF_ADD(i) prof_acc[i] += (unsigned long long)(clock64() - prof_t0);
+#define W8_PROF_FLUSH(i, slot) if (blockIdx.x == 0) g_w8a8_prof[slot] = prof_acc[i];
+#else
+#define W8_PROF_DECL
+#define W8_PROF_T0
+#define W8_PROF_ADD(i)
+#define W8_PROF_FLUSH(i, slot)
+#endif
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -105,10 +169,15 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const bool is_x = warp == 0;
             uint32_t s = 0, ph = 0;
             bool ok = true;
+            W8_PROF_DECL
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int row = is_x ? (t % p.tiles_x) * p.tile_x : (t / p.tiles_x) * kTileN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);
+                    {
+                        W8_PROF_T0
+                        ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);
+                        W8_PROF_ADD(0)
+                    }
                     if (!ok) break;
                     if (is_x) {
                         mbar_expect_tx(full + 8 * s, x_bytes);
@@ -120,22 +189,36 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
+            W8_PROF_FLUSH(0, is_x ? 0 : 1)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
+            W8_PROF_DECL
             const uint32_t idesc = make_idesc_i8((uint32_t)p.tile_x);
             uint32_t s = 0, ph = 0, it = 0;
             bool ok = true;
+#ifdef CB_TC_PROFILE
+            const long long prof_start = clock64();
+#endif
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
-                ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
+                {
+                    W8_PROF_T0
+                    ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
+                    W8_PROF_ADD(2)
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(full + 8 * s, ph, abort_flag);
+                    {
+                        W8_PROF_T0
+                        ok = mbar_wait(full + 8 * s, ph, abort_flag);
+                        W8_PROF_ADD(0)
+                    }
                     if (!ok) break;
+                    W8_PROF_T0
                     tc_fence_after();
                     const uint64_t adesc = make_kmajor_sw128_desc(sw + s * kBytesW);
                     const uint64_t bdesc = make_kmajor_sw128_desc(sx + s * kBytesX);
@@ -145,18 +228,26 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         umma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty + 8 * s);  // the stage is free once these MMAs retire
+                    W8_PROF_ADD(1)
+#ifdef CB_TC_PROFILE
+                    prof_acc[3] += 1;
+#endif
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit(tmem_full + 8 * acc);
             }
+#ifdef CB_TC_PROFILE
+            if (blockIdx.x == 0) g_w8a8_prof[6] = (unsigned long long)(clock64() - prof_start);
+#endif
+            W8_PROF_FLUSH(0, 2) W8_PROF_FLUSH(1, 3) W8_PROF_FLUSH(2, 4) W8_PROF_FLUSH(3, 5)
         }
     } else if (warp < 2 + kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
         const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes 32 * (warp % 4) .. + 31
-        T* y = static_cast<T*>(p.y);
         uint32_t it = 0;
         bool ok = true;
+        W8_PROF_DECL
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
             const int tx = t % p.tiles_x, tn = t / p.tiles_x;
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
@@ -165,34 +256,23 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const float wscale = n_ok ? load_scalar(p.ws, p.ws_dtype, n) : 0.0f;
             const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
             {
+                W8_PROF_T0
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+                W8_PROF_ADD(0)
             }
             if (!ok) break;
             tc_fence_after();
-            const int64_t m_base = (int64_t)tx * p.tile_x;
-            for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX + (uint32_t)c0, r);
-                // the 32 per-token scales of this column block: one per lane, handed round by shuffles
-                const int64_t m_lane = m_base + c0 + lane;
-                const float xs_lane = m_lane < p.M ? __ldg(p.xs + m_lane) : 0.0f;
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const float xs = __shfl_sync(0xffffffffu, xs_lane, c);
-                    const int64_t m = m_base + c0 + c;
-                    if (m >= p.M || c0 + c >= p.tile_x) continue;  // uniform across the warp
-                    float v = __fmul_rn(__fmul_rn(__int2float_rn((int)r[c]), xs), wscale);
-                    if (p.bias) v = __fadd_rn(v, bias);
-                    if (n_ok) y[m * p.ldy + n] = Widen<T>::from_float(v);
-                }
-            }
+            W8_PROF_T0
+            drain_accumulator<T>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX, (warp - 2) >> 2, kEpiWarps / 4,
+                                 (int64_t)tx * p.tile_x, n, n_ok, wscale, bias, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+            W8_PROF_ADD(1)
         }
+        if (warp == 2 && lane == 0) { W8_PROF_FLUSH(0, 7) W8_PROF_FLUSH(1, 8) }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -206,6 +286,205 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (threadIdx.x == 0 && *abort_flag) {
         atomicExch(p.error_flag, 1u);
         __nanosleep(200000);  // let any TMA copy still in flight land before the CTA's memory is released
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair version: tcgen05.mma.cta_group::2 over a cluster of two CTAs.  The pair computes 256 output
+// features x tile_x tokens per tile; each CTA loads its own 128 weight rows and only HALF of the activation
+// tile (the hardware reads operand B from both CTAs' shared memory), so a CTA pulls 32 KB per 128-k stage
+// through TMA instead of 48 KB -- the single-CTA kernel is bound by exactly that ingest.
+// Signalling: every TMA load of either CTA completes on the LEADER's (rank 0) "full" barrier -- the peer's
+// loads name the leader's barrier (the .cta_group::2 form of the TMA load allows a barrier of the peer CTA;
+// no multicast is involved) -- so the leader's MMA thread waits on one barrier per stage and nobody relays.
+// The leader frees a stage in both CTAs, and publishes a finished accumulator to both, with
+// tcgen05.commit ... .multicast::cluster; the epilogue warps of both CTAs arrive on the leader's
+// "accumulator drained" barrier.  All waits are bounded as in the single-CTA kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairBytesX = (kMaxTileX / 2) * kBlockK8;  // 16384: this CTA's half of the activation tile
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;                   // shared::cluster address -> same offset in CTA rank 0
+
+struct PairSmem {
+    static constexpr uint32_t x = 0;
+    static constexpr uint32_t w = x + kPairStages * kPairBytesX;
+    static constexpr uint32_t bars = w + kPairStages * kBytesW;
+    static constexpr uint32_t n_bars = 2 * kPairStages + 4;
+    static constexpr uint32_t tmem_slot = bars + n_bars * 8;
+    static constexpr uint32_t abort_flag = tmem_slot + 4;
+    static constexpr uint32_t total = abort_flag + 4;
+};
+constexpr uint32_t kPairSmemBytes = PairSmem::total + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same offset in CTA rank 0 (local when this CTA is rank 0)
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerMask) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_leader(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar & kPeerMask), "r"(bytes) : "memory");
+}
+// TMA tile load into THIS CTA's shared memory whose bytes are counted on the leader's barrier
+__device__ __forceinline__ void tma_load_2d_to_leader_bar(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar & kPeerMask)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive (once all prior MMAs of this thread retired) on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+// kind::i8, int32 accumulate, signed operands, K-major, M = 256 over the pair
+__device__ __forceinline__ uint32_t make_idesc_i8_pair(uint32_t n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sx = base + PairSmem::x, sw = base + PairSmem::w;
+    const uint32_t full = base + PairSmem::bars, empty = full + 8 * kPairStages;
+    const uint32_t tmem_full = empty + 8 * kPairStages, tmem_empty = tmem_full + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + PairSmem::tmem_slot);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + PairSmem::abort_flag);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (int)((p.K + kBlockK8 - 1) / kBlockK8);
+    const int total_tiles = p.tiles_x * p.tiles_n;  // tiles of 256 features x tile_x tokens
+    const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
+    const int half_x = p.tile_x / 2;
+    const uint32_t stage_bytes = (uint32_t)half_x * kBlockK8 + kBytesW;  // what ONE CTA loads per stage
+
+    if (threadIdx.x == 0) {
+        // full: one arrive.expect_tx per CTA (used on the leader only); empty: the leader's multicast commit
+        for (int i = 0; i < kPairStages; ++i) { mbar_init(full + 8 * i, 2); mbar_init(empty + 8 * i, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tmem_full + 8 * i, 1); mbar_init(tmem_empty + 8 * i, 2 * kEpiWarps); }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&map_x);
+        prefetch_tmap(&map_w);
+    }
+    if (warp == 1) tmem_alloc_pair(base + PairSmem::tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both operands of this CTA) ------------------------------
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+                const int row_x = (t % p.tiles_x) * p.tile_x + (int)rank * half_x;
+                const int row_w = (t / p.tiles_x) * 256 + (int)rank * kTileN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);  // local: freed by the leader's multicast commit
+                    if (!ok) break;
+                    mbar_expect_tx_leader(full + 8 * s, stage_bytes);
+                    tma_load_2d_to_leader_bar(sx + s * kPairBytesX, &map_x, kb * kBlockK8, row_x, full + 8 * s);
+                    tma_load_2d_to_leader_bar(sw + s * kBytesW, &map_w, kb * kBlockK8, row_w, full + 8 * s);
+                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (leader only) ------------------------------
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = make_idesc_i8_pair((uint32_t)p.tile_x);
+            uint32_t s = 0, ph = 0, it = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
+                const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+                ok = mbar_spin(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // both CTAs' epilogues drained it
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_spin(full + 8 * s, ph, abort_flag);  // arrivals and bytes come from both CTAs
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t adesc = make_kmajor_sw128_desc(sw + s * kBytesW);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(sx + s * kPairBytesX);
+#pragma unroll
+                    for (int k = 0; k < kBlockK8 / 32; ++k)
+                        umma_i8_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(empty + 8 * s);
+                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tmem_full + 8 * acc);
+            }
+        }
+    } else if (warp < 2 + kEpiWarps) {
+        // ------------------------------ epilogue (each CTA: its own 128 features) ------------------------------
+        const int quarter = warp & 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
+            const int tx = t % p.tiles_x, tn = t / p.tiles_x;
+            const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+            const int64_t n = (int64_t)tn * 256 + (int64_t)rank * kTileN + quarter * 32 + lane;
+            const bool n_ok = n < p.N;
+            const float wscale = n_ok ? load_scalar(p.ws, p.ws_dtype, n) : 0.0f;
+            const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+            {
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+            }
+            if (!ok) break;
+            tc_fence_after();
+            drain_accumulator<T>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX, (warp - 2) >> 2, kEpiWarps / 4,
+                                 (int64_t)tx * p.tile_x, n, n_ok, wscale, bias, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(tmem_empty + 8 * acc);
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer may still read this CTA's shared memory / signal its barriers until here
+    tc_fence_after();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicExch(p.error_flag, 1u);
+        __nanosleep(200000);
     }
 }
 
@@ -270,6 +549,67 @@ int pick_tile_x(int64_t M, int64_t N, int sms) {
     return best;
 }
 
+// activation rows per pair tile (a multiple of 32 <= 256: each CTA holds half) over `pairs` CTA pairs
+int pick_pair_tile_x(int64_t M, int64_t N, int pairs) {
+    const int64_t tiles_n = (N + 255) / 256;
+    int best = 256;
+    double best_cost = 1e300;
+    for (int tx = 256; tx >= 32; tx -= 32) {
+        const int64_t tiles = ((M + tx - 1) / tx) * tiles_n;
+        const double cost = (double)((tiles + pairs - 1) / pairs) * (tx + 256);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = tx; }
+    }
+    return best;
+}
+
+template <typename T>
+cudaError_t launch_pair_t(const W8A8Args& a, Params p, cudaStream_t s) {
+    const int pairs_avail = sm_count() / 2;
+    p.tile_x = pick_pair_tile_x(a.M, a.N, pairs_avail);
+    p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
+    p.tiles_n = (int)((a.N + 255) / 256);
+    CUtensorMap map_x, map_w;
+    if (!make_map_u8(&map_x, a.xq, (uint64_t)a.K, (uint64_t)a.M, (uint32_t)(p.tile_x / 2))) return cudaErrorNotSupported;
+    if (!make_map_u8(&map_w, a.wq, (uint64_t)a.K, (uint64_t)a.N, kTileN)) return cudaErrorNotSupported;
+    const int64_t tiles = (int64_t)p.tiles_x * p.tiles_n;
+    int pairs = (int)(tiles < pairs_avail ? tiles : pairs_avail);
+    auto fn = w8a8_tc_pair_kernel<T>;
+    static bool attr_done[64] = {};
+    static int max_clusters[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_done[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters[dev] == 0) {
+        // a persistent schedule needs every pair resident at once
+        int n = 0;
+        cudaLaunchConfig_t probe = cfg;
+        probe.gridDim = dim3((unsigned)(2 * pairs_avail));
+        if (cudaOccupancyMaxActiveClusters(&n, fn, &probe) != cudaSuccess || n <= 0) n = pairs_avail;
+        max_clusters[dev] = n;
+    }
+    if (pairs > max_clusters[dev]) cfg.gridDim = dim3((unsigned)(2 * max_clusters[dev]));
+    void* args[3] = {(void*)&map_x, (void*)&map_w, (void*)&p};
+    const cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)fn, args);
+    return e != cudaSuccess ? e : cudaPeekAtLastError();
+}
+
 template <typename T>
 cudaError_t launch_t(const W8A8Args& a, cudaStream_t s) {
     auto al16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
@@ -285,11 +625,16 @@ cudaError_t launch_t(const W8A8Args& a, cudaStream_t s) {
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.xs = a.xs; p.ws = a.ws; p.ws_dtype = a.ws_dtype; p.bias = a.bias; p.bias_dtype = a.bias_dtype;
     p.y = a.y; p.ldy = a.ldy;
+    p.error_flag = w8a16_tc_error_word();
+    if (!p.error_flag) return cudaErrorUnknown;
+    bool use_pair = a.M >= 256 && a.N >= 256;
+#ifdef CB_TC_DEVTOOLS
+    if (const char* f = getenv("CB_W8A8_PAIR")) use_pair = atoi(f) != 0;
+#endif
+    if (use_pair) return launch_pair_t<T>(a, p, s);
     p.tile_x = pick_tile_x(a.M, a.N, sms);
     p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
     p.tiles_n = (int)((a.N + kTileN - 1) / kTileN);
-    p.error_flag = w8a16_tc_error_word();
-    if (!p.error_flag) return cudaErrorUnknown;
     CUtensorMap map_x, map_w;
     if (!make_map_u8(&map_x, a.xq, (uint64_t)a.K, (uint64_t)a.M, (uint32_t)p.tile_x)) return cudaErrorNotSupported;
     if (!make_map_u8(&map_w, a.wq, (uint64_t)a.K, (uint64_t)a.N, kTileN)) return cudaErrorNotSupported;
@@ -316,3 +661,15 @@ cudaError_t launch_w8a8(const W8A8Args& a, cudaStream_t s) {
 }
 
 }  // namespace cb
+
+#ifdef CB_TC_PROFILE
+extern "C" int cb_dev_w8a8_profile(unsigned long long* host, int reset) {
+    cudaDeviceSynchronize();
+    int e = (int)cudaMemcpyFromSymbol(host, cb::g_w8a8_prof, sizeof(unsigned long long) * 16);
+    if (reset) {
+        unsigned long long z[16] = {0};
+        e |= (int)cudaMemcpyToSymbol(cb::g_w8a8_prof, z, sizeof(z));
+    }
+    return e;
+}
+#endif

@@ -26,6 +26,13 @@
 //               memory (canonical K-major 128-byte-swizzled UMMA layout, fence.proxy.async) or,
 //               for M <= 208, straight in tensor memory (tcgen05.st), then barrier arrive
 //
+// One operand ring: stage s carries the activation tile, the int8 tile and the widened tile of a k-block.
+// The MMA thread waits on ONE "full" barrier per k-block (TMA bytes of the activations + the eight
+// converter warps) and commits to ONE "empty" barrier, which both TMA producers wait on; the converters wait
+// on the int8 tile's barrier only (its producer has already waited for the stage).  The MMA thread's loop is
+// the critical path: an isolated test shows ~200 cycles of other work per group of four MMAs is all the
+// tensor core's queue hides, and a barrier probe costs ~100 cycles even on a completed phase.
+//
 // Schedule: tile t of round r goes to CTA t - r * gridDim.x.  A schedule without one full round
 // (fewer tiles than SMs) splits its tiles along K over the idle CTAs: every split stores its fp32
 // partial accumulator to its own slab of the workspace, and a small second kernel adds the slabs
@@ -47,6 +54,13 @@ namespace cb {
 namespace {
 
 using namespace tc;
+
+#ifndef CB_TC_PROFILE
+#define RP_DECL
+#define RP_T0
+#define RP_ADD(i)
+#define RP_FLUSH(i, slot)
+#endif
 
 // Development switches (never in the shipped build): -DCB_TC_DEVTOOLS reads CB_TC_MODE / CB_TC_NOSPLIT
 // from the environment, -DCB_TC_PROFILE records per-CTA start / end times, -DCB_TC_NOCONVERT and
@@ -82,9 +96,14 @@ enum AMode : int { kSmemA = 0, kTmemA = 1 };
 template <int MODE>
 struct Cfg {
     static constexpr int kMaxTileX = MODE == kSmemA ? 256 : 208;  // activation rows per tile = UMMA N (multiple of 16)
-    static constexpr int kStagesX = MODE == kSmemA ? 4 : 6;       // activation tiles in flight
-    static constexpr int kStagesA = 3;                             // widened weight tiles (16 KiB shared / 32 columns)
-    static constexpr int kStagesW8 = MODE == kSmemA ? 4 : 6;      // int8 weight tiles (8 KiB each)
+    // ONE operand ring: stage s holds the activation tile and the widened weight tile of a k-block, one
+    // "full" barrier (TMA bytes + the eight converter warps) and one "empty" barrier (one tcgen05.commit) per
+    // stage -- the MMA thread's loop is the critical path of the kernel, and every barrier it probes or
+    // commits to costs it time the tensor core spends idle.
+    static constexpr int kStages = MODE == kSmemA ? 4 : 3;         // kTmemA: three 32-column A stages fit tensor memory
+    static constexpr int kStagesX = kStages;
+    static constexpr int kStagesA = kStages;
+    static constexpr int kStagesW8 = kStages;                      // int8 weight tiles (8 KiB each), part of the same ring
     static constexpr int kAccStride = kMaxTileX;                   // columns between the two accumulators
     static constexpr int kACol = 2 * kMaxTileX;                    // first tensor-memory column of the A stages (kTmemA)
     static constexpr int kAColsPerStage = kBlockK / 2;             // two 16-bit k per 32-bit column
@@ -95,8 +114,8 @@ struct Cfg {
     static constexpr uint32_t a = x + kStagesX * kBytesX;
     static constexpr uint32_t w8 = a + kStagesA * kBytesA;
     static constexpr uint32_t bars = w8 + kStagesW8 * kBytesW8;
-    // barriers: full_x, empty_x, full_w8, empty_w8, full_a, empty_a, tmem_full[2], tmem_empty[2]
-    static constexpr uint32_t n_bars = 2 * kStagesX + 2 * kStagesW8 + 2 * kStagesA + 4;
+    // barriers: full[kStages], empty[kStages], full_w8[kStages], tmem_full[2], tmem_empty[2]
+    static constexpr uint32_t n_bars = 3 * kStages + 4;
     static constexpr uint32_t tmem_slot = bars + n_bars * 8;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
@@ -157,6 +176,11 @@ constexpr int kMaxKO = 64;  // outlier columns handled by the epilogue's CUDA-co
 #ifdef CB_TC_PROFILE
 // development only: per-CTA {start, end (globaltimer ns), SM id, items} of the last launch
 __device__ unsigned long long g_tc_prof[1024 * 4];
+__device__ unsigned long long g_tc_role[32];  // per-role cycle counters of CTA 0 (see the RP_ macros)
+#define RP_DECL unsigned long long rp_acc[4] = {0, 0, 0, 0};
+#define RP_T0 const long long rp_t0 = clock64();
+#define RP_ADD(i) rp_acc[i] += (unsigned long long)(clock64() - rp_t0);
+#define RP_FLUSH(i, slot) if (blockIdx.x == 0) g_tc_role[slot] = rp_acc[i];
 __device__ __forceinline__ unsigned long long prof_now() {
     unsigned long long v;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
@@ -230,10 +254,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t sx = base + C::x, sa = base + C::a, sw8 = base + C::w8;
     const uint32_t bars = base + C::bars;
-    const uint32_t full_x = bars, empty_x = full_x + 8 * kStagesX;
-    const uint32_t full_w8 = empty_x + 8 * kStagesX, empty_w8 = full_w8 + 8 * kStagesW8;
-    const uint32_t full_a = empty_w8 + 8 * kStagesW8, empty_a = full_a + 8 * kStagesA;
-    const uint32_t tmem_full = empty_a + 8 * kStagesA, tmem_empty = tmem_full + 16;
+    const uint32_t full_x = bars, empty_x = full_x + 8 * kStagesX;  // the operand ring's full / empty barriers
+    const uint32_t full_a = full_x, empty_a = empty_x;              // (the converters and the activation TMA share them)
+    const uint32_t full_w8 = empty_x + 8 * kStagesX;
+    const uint32_t tmem_full = full_w8 + 8 * kStagesW8, tmem_empty = tmem_full + 16;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + C::tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + C::abort_flag);
 
@@ -254,9 +278,8 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #endif
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStagesX; ++i) { mbar_init(full_x + 8 * i, 1); mbar_init(empty_x + 8 * i, 1); }
-        for (int i = 0; i < kStagesW8; ++i) { mbar_init(full_w8 + 8 * i, 1); mbar_init(empty_w8 + 8 * i, kConvWarps); }
-        for (int i = 0; i < kStagesA; ++i) { mbar_init(full_a + 8 * i, kConvWarps); mbar_init(empty_a + 8 * i, 1); }
+        for (int i = 0; i < kStagesX; ++i) { mbar_init(full_x + 8 * i, 1 + kConvWarps); mbar_init(empty_x + 8 * i, 1); }
+        for (int i = 0; i < kStagesW8; ++i) mbar_init(full_w8 + 8 * i, 1);
         for (int i = 0; i < 2; ++i) { mbar_init(tmem_full + 8 * i, 1); mbar_init(tmem_empty + 8 * i, kEpiWarps); }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -277,17 +300,23 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
+            RP_DECL
             WorkItem w;
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
                 const int row_x = (w.tile % p.tiles_x) * p.tile_x;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
+                    {
+                        RP_T0
+                        ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
+                        RP_ADD(0)
+                    }
                     if (!ok) break;
                     mbar_expect_tx(full_x + 8 * s, x_bytes);
                     tma_load_2d(sx + s * kBytesX, &map_x, kb * kBlockK, row_x, full_x + 8 * s);
                     if (++s == kStagesX) { s = 0; ph ^= 1u; }
                 }
             }
+            RP_FLUSH(0, 0)
         }
     } else if (warp == kW8Warp) {
         // ------------------------------ TMA producer, int8 weights ------------------------------
@@ -295,6 +324,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             constexpr int kAhead = 12;  // k-blocks of weights requested into L2 ahead of their TMA load
             uint32_t s = 0, ph = 0;
             bool ok = true;
+            RP_DECL
             WorkItem w, nx;
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
                 const int row_w = (w.tile / p.tiles_x) * kTileN;
@@ -304,43 +334,59 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     if (kb + kAhead < w.kb1) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kBlockK, row_w);
                     else if (has_next && nx.kb0 + (kb + kAhead - w.kb1) < nx.kb1)
                         tma_prefetch_l2_2d(&map_w, (nx.kb0 + kb + kAhead - w.kb1) * kBlockK, row_w_next);
-                    ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag);
+                    {
+                        // the int8 staging buffer of a stage is free when the stage is: the MMAs that retired
+                        // consumed what the converters made of it
+                        RP_T0
+                        ok = mbar_wait(empty_a + 8 * s, ph ^ 1u, abort_flag);
+                        RP_ADD(0)
+                    }
                     if (!ok) break;
                     mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
                     tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, row_w, full_w8 + 8 * s);
                     if (++s == kStagesW8) { s = 0; ph ^= 1u; }
                 }
             }
+            RP_FLUSH(0, 1)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             const uint32_t idesc = make_idesc(Widen<A>::kBf16, (uint32_t)p.tile_x);
-            // Ring positions are kept incrementally (no divisions) and the barriers of the NEXT
-            // k-block are probed before the MMAs of the current one are issued, so a probe's
-            // latency overlaps the issue; this thread's loop is the critical path of the kernel.
-            uint32_t s_a = 0, ph_a = 0, s_x = 0, ph_x = 0, it = 0;
-            bool ok = true, pre = false;
+            // This thread's loop is the critical path of the kernel: tcgen05.mma issue is not free-running
+            // (cycle counters: the four issues of a k-block take about as long as their execution), so
+            // whatever else the loop does -- barrier probes, commits -- is time the tensor core idles.
+            // Hence one wait and one commit per k-block.
+            uint32_t s_a = 0, ph_a = 0, it = 0;
+            bool ok = true;
+            RP_DECL
+#ifdef CB_TC_PROFILE
+            const long long rp_start = clock64();
+            unsigned long long rp_kb = 0, rp_issue = 0;
+#endif
             WorkItem w;
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx, ++it) {
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
-                ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
+                {
+                    RP_T0
+                    ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
+                    RP_ADD(2)
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    if (!pre) {
-                        const bool r0 = mbar_try(full_a + 8 * s_a, ph_a), r1 = mbar_try(full_x + 8 * s_x, ph_x);
-                        ok = (r0 || mbar_wait(full_a + 8 * s_a, ph_a, abort_flag)) &&
-                             (r1 || mbar_wait(full_x + 8 * s_x, ph_x, abort_flag));
-                        if (!ok) break;
+                    {
+                        RP_T0
+                        ok = mbar_wait(full_a + 8 * s_a, ph_a, abort_flag);  // activation bytes landed and weights widened
+                        RP_ADD(0)
                     }
+                    if (!ok) break;
                     tc_fence_after();
-                    uint32_t ns_a = s_a + 1, nph_a = ph_a, ns_x = s_x + 1, nph_x = ph_x;
-                    if (ns_a == kStagesA) { ns_a = 0; nph_a ^= 1u; }
-                    if (ns_x == kStagesX) { ns_x = 0; nph_x ^= 1u; }
-                    const bool n0 = mbar_try(full_a + 8 * ns_a, nph_a), n1 = mbar_try(full_x + 8 * ns_x, nph_x);
-                    const uint64_t bdesc = make_kmajor_sw128_desc(sx + s_x * kBytesX);
+#ifdef CB_TC_PROFILE
+                    const long long rp_i0 = clock64();
+#endif
+                    const uint64_t bdesc = make_kmajor_sw128_desc(sx + s_a * kBytesX);
 #ifdef CB_TC_NOMMA  // development only
                     if (p.M < 0)
 #endif
@@ -361,14 +407,20 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                                             (kb > w.kb0 || k > 0) ? 1u : 0u);
                         }
                     }
-                    umma_commit(empty_a + 8 * s_a);  // both operand slots are free once these MMAs retire
-                    umma_commit(empty_x + 8 * s_x);
-                    pre = n0 && n1;
-                    s_a = ns_a; ph_a = nph_a; s_x = ns_x; ph_x = nph_x;
+                    umma_commit(empty_a + 8 * s_a);  // the stage is free once these MMAs retire
+#ifdef CB_TC_PROFILE
+                    rp_issue += (unsigned long long)(clock64() - rp_i0);
+                    rp_kb += 1;
+#endif
+                    if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit(tmem_full + 8 * acc);  // accumulator complete -> epilogue
             }
+            RP_FLUSH(0, 2) RP_FLUSH(1, 3) RP_FLUSH(2, 5)
+#ifdef CB_TC_PROFILE
+            if (blockIdx.x == 0) { g_tc_role[4] = rp_issue; g_tc_role[6] = rp_kb; g_tc_role[7] = (unsigned long long)(clock64() - rp_start); }
+#endif
         }
     } else if (warp < 2 + kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
@@ -435,20 +487,25 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const int cw = warp - (2 + kEpiWarps);  // 0 .. 7
         uint32_t s_w = 0, ph_w = 0, s_a = 0, ph_a = 0;
         bool ok = true;
+        RP_DECL
         WorkItem w;
         for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
             for (int kb = w.kb0; kb < w.kb1; ++kb) {
                 {
                     // lane 0 probes both barriers back to back, the warp shares the verdict
+                    // one wait: the int8 tile has landed -- its producer waited for the stage to be free, so the
+                    // widened tile of this stage may be overwritten too (a probe costs ~100 cycles even on a
+                    // completed phase, and the converters' loop is as long as the MMA thread's)
                     int okw = 1;
                     if (lane == 0) {
-                        const bool r0 = mbar_try(full_w8 + 8 * s_w, ph_w), r1 = mbar_try(empty_a + 8 * s_a, ph_a ^ 1u);
-                        okw = ((r0 || mbar_wait(full_w8 + 8 * s_w, ph_w, abort_flag)) &&
-                               (r1 || mbar_wait(empty_a + 8 * s_a, ph_a ^ 1u, abort_flag))) ? 1 : 0;
+                        RP_T0
+                        okw = mbar_wait(full_w8 + 8 * s_w, ph_w, abort_flag) ? 1 : 0;
+                        RP_ADD(0)
                     }
                     ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
                 }
                 if (!ok) break;
+                RP_T0
                 tc_fence_after();
                 const uint32_t src = sw8 + s_w * kBytesW8;
                 if constexpr (MODE == kSmemA) {
@@ -503,14 +560,13 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     tc_fence_before();
                 }
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full_a + 8 * s_a);
-                    mbar_arrive(empty_w8 + 8 * s_w);
-                }
+                if (lane == 0) mbar_arrive(full_a + 8 * s_a);
+                RP_ADD(2)
                 if (++s_w == kStagesW8) { s_w = 0; ph_w ^= 1u; }
                 if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
             }
         }
+        if (lane == 0) { RP_FLUSH(0, 8 + cw) RP_FLUSH(2, 16 + cw) }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -746,6 +802,10 @@ cudaError_t w8a16_tc_read_error(unsigned int* host_value, cudaStream_t s) {
 }  // namespace cb
 
 #ifdef CB_TC_PROFILE
+extern "C" int cb_dev_tc_roles(unsigned long long* host) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, cb::g_tc_role, sizeof(unsigned long long) * 32);
+}
 extern "C" int cb_dev_tc_profile(unsigned long long* host, int ctas) {
     cudaDeviceSynchronize();
     return (int)cudaMemcpyFromSymbol(host, cb::g_tc_prof, sizeof(unsigned long long) * 4 * ctas);

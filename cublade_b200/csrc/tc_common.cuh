@@ -201,15 +201,20 @@ struct Widen;
 template <>
 struct Widen<__nv_bfloat16> {
     static constexpr bool kBf16 = true;
-    // four int8 codes -> (c0,c1), (c2,c3) as bf16 pairs; exact (see w8a16_stream.cu)
+    // four int8 codes -> (c0,c1), (c2,c3) as bf16 pairs; exact
     __device__ __forceinline__ static void four(uint32_t c, uint32_t& lo, uint32_t& hi) {
-        const uint32_t u = c ^ 0x80808080u;
-        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
-        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
-        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
-        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
-        lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
-        hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+        // bf16 magic in packed arithmetic, exact: with b the code's byte, P = 0x4300 | b per 16-bit lane;
+        // A = P with bit 7 cleared = 128 + (b & 127), C = P with only bit 7 kept = 128 or 256 (both exact bf16),
+        // and A - C = b for b < 128, b - 256 otherwise: the signed code, an integer of magnitude <= 128 that
+        // bf16 holds exactly, so the packed subtraction rounds nothing.  Two permutes, four logic ops and two
+        // packed subtractions per four codes (the fp32 route took eleven instructions).
+        const uint32_t p01 = __byte_perm(c, 0x43434343u, 0x4140), p23 = __byte_perm(c, 0x43434343u, 0x4342);
+        const uint32_t a01 = p01 & 0xFF7FFF7Fu, c01 = p01 & 0xFF80FF80u;
+        const uint32_t a23 = p23 & 0xFF7FFF7Fu, c23 = p23 & 0xFF80FF80u;
+        const __nv_bfloat162 d01 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a01), *reinterpret_cast<const __nv_bfloat162*>(&c01));
+        const __nv_bfloat162 d23 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a23), *reinterpret_cast<const __nv_bfloat162*>(&c23));
+        lo = *reinterpret_cast<const uint32_t*>(&d01);
+        hi = *reinterpret_cast<const uint32_t*>(&d23);
     }
     __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }

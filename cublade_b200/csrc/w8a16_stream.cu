@@ -35,15 +35,18 @@ template <>
 struct Act<__nv_bfloat16> {
     // four int8 codes (one word) -> two words of bf16 pairs (c0,c1) (c2,c3)
     __device__ __forceinline__ static void widen4(uint32_t c, uint32_t& lo, uint32_t& hi) {
-        // fp32 magic: 0x4B000000 | (code ^ 0x80) = 2^23 + code + 128; subtract 2^23 + 128; the
-        // result is a small integer, so its top 16 bits are its exact bf16 form.
-        const uint32_t u = c ^ 0x80808080u;
-        const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
-        const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
-        const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
-        const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
-        lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
-        hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+        // bf16 magic in packed arithmetic, exact: with b the code's byte, P = 0x4300 | b per 16-bit lane;
+        // A = P with bit 7 cleared = 128 + (b & 127), C = P with only bit 7 kept = 128 or 256 (both exact bf16),
+        // and A - C = b for b < 128, b - 256 otherwise: the signed code, an integer of magnitude <= 128 that
+        // bf16 holds exactly, so the packed subtraction rounds nothing.  Two permutes, four logic ops and two
+        // packed subtractions per four codes (the fp32 route took eleven instructions).
+        const uint32_t p01 = __byte_perm(c, 0x43434343u, 0x4140), p23 = __byte_perm(c, 0x43434343u, 0x4342);
+        const uint32_t a01 = p01 & 0xFF7FFF7Fu, c01 = p01 & 0xFF80FF80u;
+        const uint32_t a23 = p23 & 0xFF7FFF7Fu, c23 = p23 & 0xFF80FF80u;
+        const __nv_bfloat162 d01 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a01), *reinterpret_cast<const __nv_bfloat162*>(&c01));
+        const __nv_bfloat162 d23 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a23), *reinterpret_cast<const __nv_bfloat162*>(&c23));
+        lo = *reinterpret_cast<const uint32_t*>(&d01);
+        hi = *reinterpret_cast<const uint32_t*>(&d23);
     }
     __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
         asm volatile(

@@ -108,5 +108,5 @@ class cuBladeW8A16LinearLayer(nn.Module):
         return y2d.view(*lead, self.out_features)
 
 
-# BASELINE spelling (lower-case b) of the same class
+# lower-case-b spelling of the same class, used by some callers
 cubladeW8A16LinearLayer = cuBladeW8A16LinearLayer

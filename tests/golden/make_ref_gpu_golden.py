@@ -13,7 +13,7 @@ replayed on the CPU by ``tests/test_golden.py`` -- that is what pins the oracle 
 Each reference extension is exercised in a process of its own (``--stage``), one after the
 other: quantizers first, then the dequantizers on the codes the quantizers wrote.
 
-    python tests/golden/make_ref_gpu_golden.py --out gpurun_out
+    python tests/golden/make_ref_gpu_golden.py --out out_dir
 """
 from __future__ import annotations
 
@@ -168,7 +168,7 @@ def finish(work: Path, out: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out")
+    ap.add_argument("--out", default="ref_gpu_out")
     ap.add_argument("--stage", default=None, choices=STAGES)
     ap.add_argument("--work", default=None, help="scratch directory for the per-stage files")
     args = ap.parse_args()

@@ -91,16 +91,19 @@ constexpr uint32_t kBytesW8 = kTileN * kBlockK;  // 8192
 //           80 KiB of shared-memory traffic per k-block instead of 112 KiB -- at full tensor rate the
 //           shared-memory path, not the tensor core, is what saturates.  Tensor memory holds two
 //           208-column accumulators plus three 32-column A stages, so activation tiles stop at 208 rows.
-enum AMode : int { kSmemA = 0, kTmemA = 1 };
+//   kTmemA128: kTmemA for activation tiles of at most 128 rows: two 128-column accumulators leave room for eight
+//           A stages, so the operand ring is eight k-blocks deep -- with one tile per CTA (M <= 128) the kernel is
+//           a weight stream whose pace is set by how many k-blocks are in flight, not by the tensor core.
+enum AMode : int { kSmemA = 0, kTmemA = 1, kTmemA128 = 2 };
 
 template <int MODE>
 struct Cfg {
-    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : 208;  // activation rows per tile = UMMA N (multiple of 16)
+    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : (MODE == kTmemA ? 208 : 128);  // activation rows per tile = UMMA N
     // ONE operand ring: stage s holds the activation tile and the widened weight tile of a k-block, one
     // "full" barrier (TMA bytes + the eight converter warps) and one "empty" barrier (one tcgen05.commit) per
     // stage -- the MMA thread's loop is the critical path of the kernel, and every barrier it probes or
     // commits to costs it time the tensor core spends idle.
-    static constexpr int kStages = MODE == kSmemA ? 4 : 3;         // kTmemA: three 32-column A stages fit tensor memory
+    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 3 : 8);  // kTmemA: three 32-column A stages fit
     static constexpr int kStagesX = kStages;
     static constexpr int kStagesA = kStages;
     static constexpr int kStagesW8 = kStages;                      // int8 weight tiles (8 KiB each), part of the same ring
@@ -701,13 +704,14 @@ static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, i
 // Mode: measured on B200 (N = 14336, K = 4096) the tensor-memory route is 7-10 % ahead while one
 // activation tile of <= 208 rows covers M, and behind from there on (its tiles are 208 rows, not 256).
 static TcPlan make_plan(int64_t M, int64_t N, int64_t K, int sms, bool may_split) {
-    int mode = M <= Cfg<kTmemA>::kMaxTileX ? kTmemA : kSmemA;
+    int mode = M <= Cfg<kTmemA128>::kMaxTileX ? kTmemA128 : (M <= Cfg<kTmemA>::kMaxTileX ? kTmemA : kSmemA);
 #ifdef CB_TC_DEVTOOLS
-    if (const char* f = getenv("CB_TC_MODE")) mode = atoi(f) == kTmemA ? kTmemA : kSmemA;
+    if (const char* f = getenv("CB_TC_MODE")) mode = atoi(f);
 #endif
     TcPlan best{};
     double best_cost = 1e300;
-    for (int tx = (mode == kSmemA ? Cfg<kSmemA>::kMaxTileX : Cfg<kTmemA>::kMaxTileX); tx >= 32; tx -= 16) {
+    const int max_tx = mode == kSmemA ? Cfg<kSmemA>::kMaxTileX : (mode == kTmemA ? Cfg<kTmemA>::kMaxTileX : Cfg<kTmemA128>::kMaxTileX);
+    for (int tx = max_tx; tx >= 32; tx -= 16) {
         double cost;
         const TcPlan pl = plan_for_tile(mode, tx, M, N, K, sms, may_split, &cost);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = pl; }
@@ -781,8 +785,10 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     cudaError_t e;
     if (pl.mode == kSmemA) e = bf16 ? launch_variant<__nv_bfloat16, kSmemA>(map_x, map_w, p, grid, s)
                                     : launch_variant<__half, kSmemA>(map_x, map_w, p, grid, s);
-    else e = bf16 ? launch_variant<__nv_bfloat16, kTmemA>(map_x, map_w, p, grid, s)
-                  : launch_variant<__half, kTmemA>(map_x, map_w, p, grid, s);
+    else if (pl.mode == kTmemA) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA>(map_x, map_w, p, grid, s)
+                                         : launch_variant<__half, kTmemA>(map_x, map_w, p, grid, s);
+    else e = bf16 ? launch_variant<__nv_bfloat16, kTmemA128>(map_x, map_w, p, grid, s)
+                  : launch_variant<__half, kTmemA128>(map_x, map_w, p, grid, s);
     if (e != cudaSuccess || pl.splits <= 1) return e;
     const unsigned fix_grid = (unsigned)(pl.rem_tiles * ((pl.tile_x + 7) / 8));
     if (bf16) w8a16_tc_fixup_kernel<__nv_bfloat16><<<fix_grid, 256, 0, s>>>(p, pl.grid);

@@ -78,8 +78,10 @@ struct WidenDev {
 constexpr int kTileN = 128;  // weight rows (output features) per tile = UMMA M
 constexpr int kConvWarps = 8;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (3 + kEpiWarps + kConvWarps) * 32;  // + TMA(x), MMA, TMA(w8)
-constexpr int kW8Warp = 2 + kEpiWarps + kConvWarps;         // last warp: int8 weight producer
+constexpr int kThreads = (4 + kEpiWarps + kConvWarps) * 32;  // + TMA(x), MMA, TMA(w8), second MMA issuer
+constexpr int kW8Warp = 2 + kEpiWarps + kConvWarps;         // int8 weight producer
+constexpr int kPfBlocks = 4;                                // k-blocks of weights per L2 prefetch
+constexpr int kMma2Warp = kW8Warp + 1;                      // second MMA issuer (kTmemA128 only, idle otherwise)
 constexpr int kTmemCols = 512;
 constexpr uint32_t kBytesW8 = kTileN * kBlockK;  // 8192
 
@@ -94,16 +96,30 @@ constexpr uint32_t kBytesW8 = kTileN * kBlockK;  // 8192
 //   kTmemA128: kTmemA for activation tiles of at most 128 rows: two 128-column accumulators leave room for eight
 //           A stages, so the operand ring is eight k-blocks deep -- with one tile per CTA (M <= 128) the kernel is
 //           a weight stream whose pace is set by how many k-blocks are in flight, not by the tensor core.
-enum AMode : int { kSmemA = 0, kTmemA = 1, kTmemA128 = 2 };
+//   kTmemA64: the same for tiles of at most 64 rows: twelve stages.
+enum AMode : int { kSmemA = 0, kTmemA = 1, kTmemA128 = 2, kTmemA64 = 3 };
 
 template <int MODE>
 struct Cfg {
-    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : (MODE == kTmemA ? 208 : 128);  // activation rows per tile = UMMA N
+    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : (MODE == kTmemA ? 208 : (MODE == kTmemA128 ? 128 : 64));  // activation rows per tile = UMMA N
     // ONE operand ring: stage s holds the activation tile and the widened weight tile of a k-block, one
     // "full" barrier (TMA bytes + the eight converter warps) and one "empty" barrier (one tcgen05.commit) per
     // stage -- the MMA thread's loop is the critical path of the kernel, and every barrier it probes or
     // commits to costs it time the tensor core spends idle.
-    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 3 : 8);  // kTmemA: three 32-column A stages fit
+    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 3 : (MODE == kTmemA128 ? 8 : 12));  // kTmemA: three 32-column A stages fit
+    // kTmemA128 has TWO MMA issuers: a thread needs ~350 cycles to issue the four MMAs of a k-block and commit
+    // them, whatever their size, so with short activation tiles one issuer, not the tensor core, sets the pace.
+    // Issuer i takes the k-blocks of parity i of a work item and accumulates into accumulator i; the epilogue adds
+    // the two (the accumulators then do not alternate between tiles: short tiles drain in a few hundred cycles).
+    static constexpr bool kDual = MODE >= kTmemA128;
+    // ... and THREE converter groups of four warps (one warp per tensor-memory lane quarter, the whole 64 k of
+    // its 32 weight rows), each taking every third k-block: a warp's chain per k-block -- barrier probe, shared-
+    // memory loads, widening, tcgen05.st, wait::st, fence, arrive -- is ~600 cycles of mostly latency, and with all
+    // eight converter warps working on the SAME k-block that chain, not the memory system, paced the kernel
+    // (timing floors: no change with 8 or 128 weight rows per TMA box, 12 instead of 8 stages, or no MMAs).
+    // The third group are the epilogue warps, idle during a tile's main loop in these modes.
+    static constexpr int kConvGroups = 3;
+    static constexpr int kFullArrivals = kDual ? 1 + 4 : 1 + kConvWarps;  // TMA expect_tx + converter warps per stage
     static constexpr int kStagesX = kStages;
     static constexpr int kStagesA = kStages;
     static constexpr int kStagesW8 = kStages;                      // int8 weight tiles (8 KiB each), part of the same ring
@@ -149,6 +165,7 @@ struct TcParams {
     float* partial;   // [rem_tiles][splits][tile_x][128] fp32 partial products (splits > 1)
 #ifdef CB_TC_DEVTOOLS
     int dev_x_rows;   // development only: rows actually fetched per activation stage (0 = tile_x)
+    int dev_w_rows;   // development only: rows actually fetched per int8 weight stage (0 = 128; wrong results)
 #endif
 };
 
@@ -194,11 +211,20 @@ __device__ __forceinline__ unsigned long long prof_now() {
 // Epilogue of one K-split of a tile (one warp = 32 output features x tile_x rows): store the fp32
 // partial accumulator to this split's slab, [row][feature] so that a warp writes 128 contiguous
 // bytes per row.  Kept out of line: the code of the ordinary epilogue is not affected by it.
-__device__ __noinline__ void epilogue_split(const TcParams& p, uint32_t taddr, int slab, int n_local, int64_t m_base) {
+// second_offset > 0: the partial product is the sum of two accumulators that many columns apart.
+__device__ __noinline__ void epilogue_split(const TcParams& p, uint32_t taddr, uint32_t second_offset, int slab, int n_local,
+                                            int64_t m_base) {
     float* part = p.partial + (size_t)slab * ((size_t)p.tile_x * kTileN) + n_local;
     for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + (uint32_t)c0, r);
+        if (second_offset) {
+            uint32_t r2[32];
+            tmem_ld32(taddr + second_offset + (uint32_t)c0, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(r2[c]));
+        }
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -247,6 +273,7 @@ __global__ void __launch_bounds__(256) w8a16_tc_fixup_kernel(const __grid_consta
 template <typename A, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_pf,
                 const __grid_constant__ TcParams p) {
     using C = Cfg<MODE>;
     constexpr int kStagesX = C::kStagesX, kStagesA = C::kStagesA, kStagesW8 = C::kStagesW8;
@@ -281,19 +308,60 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #endif
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStagesX; ++i) { mbar_init(full_x + 8 * i, 1 + kConvWarps); mbar_init(empty_x + 8 * i, 1); }
+        for (int i = 0; i < kStagesX; ++i) { mbar_init(full_x + 8 * i, C::kFullArrivals); mbar_init(empty_x + 8 * i, 1); }
         for (int i = 0; i < kStagesW8; ++i) mbar_init(full_w8 + 8 * i, 1);
         for (int i = 0; i < 2; ++i) { mbar_init(tmem_full + 8 * i, 1); mbar_init(tmem_empty + 8 * i, kEpiWarps); }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_x);
         prefetch_tmap(&map_w);
+        prefetch_tmap(&map_pf);
     }
     if (warp == 1) tmem_alloc(base + C::tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+
+    // kDual modes: widen the k-blocks of work item w that belong to converter group `group` (every kConvGroups-th
+    // k-block of the CTA's running count) into their tensor-memory stages.  State of the calling warp: ring stage,
+    // phase and the running count modulo kConvGroups.  Returns false when a wait gave up.
+    uint32_t cv_s = 0, cv_ph = 0, cv_g = 0;
+    auto convert_item_tmem = [&](const WorkItem& w, uint32_t group) -> bool {
+        const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes 32 * (warp % 4) .. + 31
+        const int row = quarter * 32 + lane;
+        const uint32_t swz = (uint32_t)((row >> 1) & 3);  // 64-byte TMA swizzle: chunk c of row r sits at c ^ ((r >> 1) & 3)
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+            if (cv_g == group) {
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(full_w8 + 8 * cv_s, cv_ph, abort_flag) ? 1 : 0;
+                if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
+                tc_fence_after();
+                const uint32_t rbase = sw8 + cv_s * kBytesW8 + (uint32_t)(row * 64);
+#pragma unroll
+                for (int khalf = 0; khalf < 2; ++khalf) {
+                    uint32_t c[8];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(c[4 * j]), "=r"(c[4 * j + 1]), "=r"(c[4 * j + 2]), "=r"(c[4 * j + 3])
+                                     : "r"(rbase + ((((uint32_t)(2 * khalf + j)) ^ swz) << 4)));
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) CB_WIDEN<A>::four(c[j], o[2 * j], o[2 * j + 1]);
+                    tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                  (uint32_t)(C::kACol + cv_s * C::kAColsPerStage + khalf * 16), o);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a + 8 * cv_s);
+            }
+            if (++cv_g == (uint32_t)C::kConvGroups) cv_g = 0;
+            if (++cv_s == (uint32_t)C::kStages) { cv_s = 0; cv_ph ^= 1u; }
+        }
+        return true;
+    };
 
     if (warp == 0) {
         // ------------------------------ TMA producer, activations ------------------------------
@@ -334,9 +402,14 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const bool has_next = work_item(p, num_kb, idx + 1, nx);
                 const int row_w_next = has_next ? (nx.tile / p.tiles_x) * kTileN : 0;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    if (kb + kAhead < w.kb1) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kBlockK, row_w);
-                    else if (has_next && nx.kb0 + (kb + kAhead - w.kb1) < nx.kb1)
-                        tma_prefetch_l2_2d(&map_w, (nx.kb0 + kb + kAhead - w.kb1) * kBlockK, row_w_next);
+                    // One prefetch covers kPfBlocks k-blocks (a wider box of the same tensor): every instruction
+                    // of this thread costs 100-250 cycles of issue, and with a prefetch per k-block its loop
+                    // (~600 cycles) paced the whole kernel for short activation tiles.
+                    if (((kb - w.kb0) & (kPfBlocks - 1)) == 0) {
+                        if (kb + kAhead < w.kb1) tma_prefetch_l2_2d(&map_pf, (kb + kAhead) * kBlockK, row_w);
+                        else if (has_next && nx.kb0 + (kb + kAhead - w.kb1) < nx.kb1)
+                            tma_prefetch_l2_2d(&map_pf, (nx.kb0 + kb + kAhead - w.kb1) * kBlockK, row_w_next);
+                    }
                     {
                         // the int8 staging buffer of a stage is free when the stage is: the MMAs that retired
                         // consumed what the converters made of it
@@ -345,16 +418,21 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         RP_ADD(0)
                     }
                     if (!ok) break;
+#ifdef CB_TC_DEVTOOLS
+                    mbar_expect_tx(full_w8 + 8 * s, p.dev_w_rows > 0 ? (uint32_t)(p.dev_w_rows * kBlockK) : kBytesW8);
+#else
                     mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
+#endif
                     tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, row_w, full_w8 + 8 * s);
                     if (++s == kStagesW8) { s = 0; ph ^= 1u; }
                 }
             }
             RP_FLUSH(0, 1)
         }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
+    } else if (warp == 1 || (C::kDual && warp == kMma2Warp)) {
+        // ------------------------------ MMA issuer(s) ------------------------------
         if (lane == 0) {
+            const uint32_t me = warp == 1 ? 0u : 1u;  // kDual: issuer `me` owns accumulator `me` and the k-blocks of parity `me`
             const uint32_t idesc = make_idesc(Widen<A>::kBf16, (uint32_t)p.tile_x);
             // This thread's loop is the critical path of the kernel: tcgen05.mma issue is not free-running
             // (cycle counters: the four issues of a k-block take about as long as their execution), so
@@ -369,7 +447,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #endif
             WorkItem w;
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx, ++it) {
-                const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+                const uint32_t acc = C::kDual ? me : (it & 1u), acc_ph = C::kDual ? (it & 1u) : ((it >> 1) & 1u);
                 {
                     RP_T0
                     ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
@@ -379,6 +457,11 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                    if (C::kDual && (uint32_t)((kb - w.kb0) & 1) != me) {  // the other issuer's k-block: only keep step with the ring
+                        if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
+                        continue;
+                    }
+                    const int kb_first = C::kDual ? w.kb0 + (int)me : w.kb0;  // first k-block into this accumulator
                     {
                         RP_T0
                         ok = mbar_wait(full_a + 8 * s_a, ph_a, abort_flag);  // activation bytes landed and weights widened
@@ -399,7 +482,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         for (int k = 0; k < kBlockK / 16; ++k) {
                             // +32 bytes per 16-element k step: +2 in the (>>4) start-address field
                             umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                                     (kb > w.kb0 || k > 0) ? 1u : 0u);
+                                     (kb > kb_first || k > 0) ? 1u : 0u);
                         }
                     } else {
                         const uint32_t a_tmem = tmem_base + C::kACol + s_a * C::kAColsPerStage;
@@ -407,7 +490,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         for (int k = 0; k < kBlockK / 16; ++k) {
                             // 16 k = 8 columns of A, 32 bytes of every B row
                             umma_f16_tmem_a(d_tmem, a_tmem + (uint32_t)(8 * k), bdesc + (uint64_t)(2 * k), idesc,
-                                            (kb > w.kb0 || k > 0) ? 1u : 0u);
+                                            (kb > kb_first || k > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(empty_a + 8 * s_a);  // the stage is free once these MMAs retire
@@ -418,11 +501,13 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(tmem_full + 8 * acc);  // accumulator complete -> epilogue
+                // accumulator complete -> epilogue (an issuer whose parity had no k-block in this item commits nothing
+                // pending: the barrier completes at once and the epilogue ignores that accumulator)
+                umma_commit(tmem_full + 8 * acc);
             }
-            RP_FLUSH(0, 2) RP_FLUSH(1, 3) RP_FLUSH(2, 5)
 #ifdef CB_TC_PROFILE
-            if (blockIdx.x == 0) { g_tc_role[4] = rp_issue; g_tc_role[6] = rp_kb; g_tc_role[7] = (unsigned long long)(clock64() - rp_start); }
+            if (me == 0) { RP_FLUSH(0, 2) RP_FLUSH(1, 3) RP_FLUSH(2, 5) }
+            if (blockIdx.x == 0 && me == 0) { g_tc_role[4] = rp_issue; g_tc_role[6] = rp_kb; g_tc_role[7] = (unsigned long long)(clock64() - rp_start); }
 #endif
         }
     } else if (warp < 2 + kEpiWarps) {
@@ -435,8 +520,14 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         bool ok = true;
         WorkItem w;
         for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx, ++it) {
+            if constexpr (C::kDual) {
+                // third converter group during the tile's main loop, epilogue afterwards
+                if (!convert_item_tmem(w, 2u)) { ok = false; break; }
+            }
             const int tx = w.tile % p.tiles_x, tn = w.tile / p.tiles_x;
-            const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+            // kDual: both accumulators belong to this tile (one per MMA issuer), the same barrier phase on both
+            const uint32_t acc = C::kDual ? 0u : (it & 1u), acc_ph = C::kDual ? (it & 1u) : ((it >> 1) & 1u);
+            const uint32_t second = (C::kDual && w.kb1 - w.kb0 >= 2) ? (uint32_t)C::kAccStride : 0u;  // issuer 1 had work
             const int n_local = quarter * 32 + lane;
             const int64_t n = (int64_t)tn * kTileN + n_local;
             const bool n_ok = n < p.N;
@@ -444,7 +535,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
             {
                 int okw = 1;
-                if (lane == 0) okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
+                if (lane == 0) {
+                    okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
+                    if (C::kDual && okw) okw = mbar_wait(tmem_full + 8, acc_ph, abort_flag) ? 1 : 0;
+                }
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
             }
             if (!ok) break;
@@ -454,15 +548,27 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (w.split_slot >= 0) {
                 // a K-split of a tile of the last round: rare path, kept out of line so that the code of
                 // the ordinary epilogue below is not affected by it
-                epilogue_split(p, taddr, w.split_slot, n_local, m_base);
+                epilogue_split(p, taddr, second, w.split_slot, n_local, m_base);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+                if (lane == 0) {
+                    mbar_arrive(tmem_empty + 8 * acc);
+                    if (C::kDual) mbar_arrive(tmem_empty + 8);
+                }
                 continue;
             }
             for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
+                if constexpr (C::kDual) {
+                    if (second) {
+                        uint32_t r2[32];
+                        tmem_ld32(taddr + second + (uint32_t)c0, r2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(r2[c]));
+                    }
+                }
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
@@ -483,7 +589,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+            if (lane == 0) {
+                mbar_arrive(tmem_empty + 8 * acc);
+                if (C::kDual) mbar_arrive(tmem_empty + 8);
+            }
         }
     } else if (warp < kW8Warp) {
         // ------------------------------ converters ------------------------------
@@ -492,6 +601,9 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         bool ok = true;
         RP_DECL
         WorkItem w;
+        if constexpr (C::kDual) {
+            for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) ok = convert_item_tmem(w, (uint32_t)(cw >> 2));
+        } else
         for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
             for (int kb = w.kb0; kb < w.kb1; ++kb) {
                 {
@@ -704,13 +816,19 @@ static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, i
 // Mode: measured on B200 (N = 14336, K = 4096) the tensor-memory route is 7-10 % ahead while one
 // activation tile of <= 208 rows covers M, and behind from there on (its tiles are 208 rows, not 256).
 static TcPlan make_plan(int64_t M, int64_t N, int64_t K, int sms, bool may_split) {
-    int mode = M <= Cfg<kTmemA128>::kMaxTileX ? kTmemA128 : (M <= Cfg<kTmemA>::kMaxTileX ? kTmemA : kSmemA);
+    int mode = M <= Cfg<kTmemA64>::kMaxTileX    ? kTmemA64
+               : M <= Cfg<kTmemA128>::kMaxTileX ? kTmemA128
+               : M <= Cfg<kTmemA>::kMaxTileX    ? kTmemA
+                                                : kSmemA;
 #ifdef CB_TC_DEVTOOLS
     if (const char* f = getenv("CB_TC_MODE")) mode = atoi(f);
 #endif
     TcPlan best{};
     double best_cost = 1e300;
-    const int max_tx = mode == kSmemA ? Cfg<kSmemA>::kMaxTileX : (mode == kTmemA ? Cfg<kTmemA>::kMaxTileX : Cfg<kTmemA128>::kMaxTileX);
+    const int max_tx = mode == kSmemA ? Cfg<kSmemA>::kMaxTileX
+                       : mode == kTmemA  ? Cfg<kTmemA>::kMaxTileX
+                       : mode == kTmemA128 ? Cfg<kTmemA128>::kMaxTileX
+                                           : Cfg<kTmemA64>::kMaxTileX;
     for (int tx = max_tx; tx >= 32; tx -= 16) {
         double cost;
         const TcPlan pl = plan_for_tile(mode, tx, M, N, K, sms, may_split, &cost);
@@ -725,7 +843,8 @@ size_t w8a16_tc_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 template <typename A, int MODE>
-static cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, const TcParams& p, unsigned grid,
+static cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, const CUtensorMap& map_pf,
+                                  const TcParams& p, unsigned grid,
                                   cudaStream_t s) {
     using C = Cfg<MODE>;
     // the opt-in shared-memory size is a per-device function attribute
@@ -738,7 +857,7 @@ static cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& m
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    w8a16_tc_kernel<A, MODE><<<grid, kThreads, C::kSmemBytes, s>>>(map_x, map_w, p);
+    w8a16_tc_kernel<A, MODE><<<grid, kThreads, C::kSmemBytes, s>>>(map_x, map_w, map_pf, p);
     return cudaPeekAtLastError();
 }
 
@@ -765,30 +884,38 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     p.error_flag = error_word();
     if (!p.error_flag) return cudaErrorUnknown;
 
-    uint32_t x_box_rows = (uint32_t)p.tile_x;
+    uint32_t x_box_rows = (uint32_t)p.tile_x, w_box_rows = kTileN;
 #ifdef CB_TC_DEVTOOLS
     p.dev_x_rows = getenv("CB_TC_XROWS") ? atoi(getenv("CB_TC_XROWS")) : 0;
     if (p.dev_x_rows > 0) x_box_rows = (uint32_t)p.dev_x_rows;
+    p.dev_w_rows = getenv("CB_TC_WROWS") ? atoi(getenv("CB_TC_WROWS")) : 0;
+    if (p.dev_w_rows > 0) w_box_rows = (uint32_t)p.dev_w_rows;
 #endif
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x, map_w, map_pf;
     const CUtensorMapDataType xdt = a.act_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     if (!make_map_2d(&map_x, xdt, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx * 2, kBlockK, x_box_rows,
                      CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorNotSupported;
     // the int8 tile is read by generic loads: plain rows for kSmemA, the 64-byte swizzle for kTmemA
     if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK,
-                     kTileN, pl.mode == kSmemA ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_64B))
+                     w_box_rows, pl.mode == kSmemA ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_64B))
+        return cudaErrorNotSupported;
+    // the same tensor with a box of kPfBlocks k-blocks, for L2 prefetches only (nothing lands in shared memory)
+    if (!make_map_2d(&map_pf, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K,
+                     a.K >= kPfBlocks * kBlockK ? kPfBlocks * kBlockK : kBlockK, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorNotSupported;
 
     const unsigned grid = (unsigned)pl.grid;
     const bool bf16 = a.act_dtype == kBF16;
     cudaError_t e;
-    if (pl.mode == kSmemA) e = bf16 ? launch_variant<__nv_bfloat16, kSmemA>(map_x, map_w, p, grid, s)
-                                    : launch_variant<__half, kSmemA>(map_x, map_w, p, grid, s);
-    else if (pl.mode == kTmemA) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA>(map_x, map_w, p, grid, s)
-                                         : launch_variant<__half, kTmemA>(map_x, map_w, p, grid, s);
-    else e = bf16 ? launch_variant<__nv_bfloat16, kTmemA128>(map_x, map_w, p, grid, s)
-                  : launch_variant<__half, kTmemA128>(map_x, map_w, p, grid, s);
+    if (pl.mode == kSmemA) e = bf16 ? launch_variant<__nv_bfloat16, kSmemA>(map_x, map_w, map_pf, p, grid, s)
+                                    : launch_variant<__half, kSmemA>(map_x, map_w, map_pf, p, grid, s);
+    else if (pl.mode == kTmemA) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA>(map_x, map_w, map_pf, p, grid, s)
+                                         : launch_variant<__half, kTmemA>(map_x, map_w, map_pf, p, grid, s);
+    else if (pl.mode == kTmemA128) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA128>(map_x, map_w, map_pf, p, grid, s)
+                                            : launch_variant<__half, kTmemA128>(map_x, map_w, map_pf, p, grid, s);
+    else e = bf16 ? launch_variant<__nv_bfloat16, kTmemA64>(map_x, map_w, map_pf, p, grid, s)
+                  : launch_variant<__half, kTmemA64>(map_x, map_w, map_pf, p, grid, s);
     if (e != cudaSuccess || pl.splits <= 1) return e;
     const unsigned fix_grid = (unsigned)(pl.rem_tiles * ((pl.tile_x + 7) / 8));
     if (bf16) w8a16_tc_fixup_kernel<__nv_bfloat16><<<fix_grid, 256, 0, s>>>(p, pl.grid);

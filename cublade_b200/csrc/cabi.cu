@@ -251,6 +251,52 @@ int32_t cb_w8a8_linear(const void* xq, const float* x_scales, int64_t M, int64_t
     return cuda_result(cb::launch_w8a8(a, as_stream(stream)), "cb_w8a8_linear", 1);
 }
 
+int32_t cb_w4_quantize_rows(const void* w, int32_t dtype, int64_t N, int64_t K, float eps, void* packed, float* scale_out,
+                            void* stream) {
+    if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "cb_w4_quantize_rows: w must be float16, bfloat16 or float32");
+    if (N < 0 || K < 0) return fail(CB_ERR_ARGUMENT, "cb_w4_quantize_rows: negative size");
+    if (K % 8 != 0) return fail(CB_ERR_ARGUMENT, "cb_w4_quantize_rows: K must be a multiple of 8");
+    if (N == 0 || K == 0) return CB_OK;
+    if (!w || !packed || !scale_out) return fail(CB_ERR_ARGUMENT, "cb_w4_quantize_rows: null pointer");
+    return cuda_result(cb::launch_w4_quantize_rows(w, dtype, N, K, eps, packed, scale_out, as_stream(stream)),
+                       "cb_w4_quantize_rows", 1);
+}
+
+int32_t cb_w4_unpack(const void* packed, int64_t N, int64_t K, void* codes_int8, void* stream) {
+    if (N < 0 || K < 0) return fail(CB_ERR_ARGUMENT, "cb_w4_unpack: negative size");
+    if (K % 8 != 0) return fail(CB_ERR_ARGUMENT, "cb_w4_unpack: K must be a multiple of 8");
+    if (N == 0 || K == 0) return CB_OK;
+    if (!packed || !codes_int8) return fail(CB_ERR_ARGUMENT, "cb_w4_unpack: null pointer");
+    if (reinterpret_cast<uintptr_t>(codes_int8) % 8) return fail(CB_ERR_ARGUMENT, "cb_w4_unpack: output must be 8-byte aligned");
+    return cuda_result(cb::launch_w4_unpack(packed, N, K, static_cast<int8_t*>(codes_int8), as_stream(stream)),
+                       "cb_w4_unpack", 1);
+}
+
+size_t cb_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) { return cb::w4a16_workspace_bytes(M, N, K, false); }
+
+int32_t cb_w4a16_linear(const void* x, int32_t act_dtype, int64_t M, int64_t K, int64_t ldx, const void* wq4, int64_t N,
+                        const void* scales, int32_t scales_dtype, const void* bias, int32_t bias_dtype, void* y,
+                        int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!is_half_like(act_dtype)) return fail(CB_ERR_DTYPE, "cb_w4a16_linear: activations must be float16 or bfloat16");
+    if (!is_float_like(scales_dtype) || (bias && !is_float_like(bias_dtype)))
+        return fail(CB_ERR_DTYPE, "cb_w4a16_linear: scales / bias must be float16, bfloat16 or float32");
+    if (M < 0 || N < 0 || K < 0) return fail(CB_ERR_ARGUMENT, "cb_w4a16_linear: negative size");
+    if (M == 0 || N == 0) return CB_OK;
+    if (K == 0 || K % 8 != 0) return fail(CB_ERR_ARGUMENT, "cb_w4a16_linear: K must be a positive multiple of 8");
+    if (!x || !wq4 || !scales || !y) return fail(CB_ERR_ARGUMENT, "cb_w4a16_linear: null pointer");
+    if (ldx < K || ldy < N) return fail(CB_ERR_ARGUMENT, "cb_w4a16_linear: row stride smaller than the row");
+    cb::W4A16Args a;
+    a.x = x; a.M = M; a.K = K; a.ldx = ldx; a.wq4 = wq4; a.N = N;
+    a.scales = scales; a.scales_dtype = scales_dtype; a.bias = bias; a.bias_dtype = bias_dtype;
+    a.y = y; a.ldy = ldy; a.act_dtype = act_dtype; a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+    int launches = 0;
+    const cudaError_t e = cb::launch_w4a16(a, as_stream(stream), &launches);
+    if (e == cudaErrorInvalidValue)
+        return fail(CB_ERR_ARGUMENT, "cb_w4a16_linear: this shape needs cb_w4a16_workspace_bytes(M, N, K) bytes of 16-byte "
+                                     "aligned workspace");
+    return cuda_result(e, "cb_w4a16_linear", launches);
+}
+
 int32_t cb_quantize_per_axis_int8(const void* x, int32_t dtype, int64_t outer, int64_t C, int64_t inner, float eps, void* q,
                                   float* scale, float* scratch, void* stream) {
     if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "cb_quantize_per_axis_int8: x must be float16, bfloat16 or float32");

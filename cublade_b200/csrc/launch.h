@@ -92,6 +92,29 @@ struct W8A8Args {
 };
 cudaError_t launch_w8a8(const W8A8Args& a, cudaStream_t s);
 
+// ---- W4A16 linear (4-bit weights, packed eight codes per 32-bit word: byte j = code j | code 4 + j << 4) ----
+// w [N, K] fp16 / bf16 / fp32 -> packed [N, K / 2] + scale_out [N]; K % 8 == 0.
+cudaError_t launch_w4_quantize_rows(const void* w, int dtype, int64_t N, int64_t K, float eps, void* packed,
+                                    float* scale_out, cudaStream_t s);
+cudaError_t launch_w4_unpack(const void* packed, int64_t N, int64_t K, int8_t* out, cudaStream_t s);
+struct W4A16Args {
+    const void* x;       // [M, K] bf16 / f16, row stride ldx elements
+    int64_t M, K, ldx;
+    const void* wq4;     // [N, K / 2] packed codes
+    int64_t N;
+    const void* scales;  // [N]
+    int scales_dtype;
+    const void* bias;    // [N] or nullptr
+    int bias_dtype;
+    void* y;             // [M, N] of the activation type
+    int64_t ldy;
+    int act_dtype;
+    void* workspace;
+    size_t workspace_bytes;
+};
+size_t w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, bool aligned);
+cudaError_t launch_w4a16(const W4A16Args& a, cudaStream_t s, int* launches);
+
 // ---- dense GEMM C[M, N] = A[M, K] . B[K, N] (fp16 / bf16 -> fp32 accumulate, int8 / uint8 -> int32) ----------
 // in_kind: 0 fp16, 1 bf16, 2 int8, 3 uint8.  out_kind: 0 fp32, 1 fp16 (fp16 inputs only), 2 int32.
 // workspace: tc_gemm_workspace_bytes(N, K, in_kind) bytes for the transposed copy of B.

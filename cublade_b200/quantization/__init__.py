@@ -6,6 +6,7 @@ from .linear import cuBladeW8A16LinearLayer, cubladeW8A16LinearLayer
 from .quantizers import quantize_tensor, quantize_model
 from .outlier_utils import detect_outlier_columns, separate_outliers, split_weights_by_outliers
 from .fused import rmsnorm_quantize_tensor
+from .linear_w4a16 import cuBladeW4A16LinearLayer
 from .linear_w8a8 import cuBladeW8A8LinearLayer
 from .checkpoint import load_quantized_model, load_quantized_state_dict, save_quantized_model
 
@@ -20,6 +21,7 @@ __all__ = [
     "separate_outliers",
     "split_weights_by_outliers",
     "rmsnorm_quantize_tensor",
+    "cuBladeW4A16LinearLayer",
     "cuBladeW8A8LinearLayer",
     "save_quantized_model",
     "load_quantized_model",

@@ -23,27 +23,30 @@ import torch
 import torch.nn as nn
 
 FORMAT_VERSION = 1
-_ROW_SHARDED = ("int8_weights", "scales", "outlier_weights", "bias")
+_ROW_SHARDED = ("int8_weights", "int4_weights", "scales", "outlier_weights", "bias")
 _REPLICATED = ("normal_cols", "outlier_cols")
 
 
 def _quantized_layers(model: nn.Module):
     from .linear import cuBladeW8A16LinearLayer
+    from .linear_w4a16 import cuBladeW4A16LinearLayer
     from .linear_w8a8 import cuBladeW8A8LinearLayer
 
     for name, module in model.named_modules():
-        if isinstance(module, (cuBladeW8A16LinearLayer, cuBladeW8A8LinearLayer)):
+        if isinstance(module, (cuBladeW8A16LinearLayer, cuBladeW8A8LinearLayer, cuBladeW4A16LinearLayer)):
             yield name, module
 
 
 def quantized_layer_manifest(model: nn.Module) -> Dict[str, Dict[str, Any]]:
     """What is needed to rebuild the quantized layers of ``model`` without the original weights."""
+    from .linear_w4a16 import cuBladeW4A16LinearLayer
     from .linear_w8a8 import cuBladeW8A8LinearLayer
 
     out = {}
     for name, m in _quantized_layers(model):
         out[name] = {
-            "quant_type": "w8a8" if isinstance(m, cuBladeW8A8LinearLayer) else "w8a16",
+            "quant_type": ("w8a8" if isinstance(m, cuBladeW8A8LinearLayer) else
+                           "w4a16" if isinstance(m, cuBladeW4A16LinearLayer) else "w8a16"),
             "in_features": m.in_features, "out_features": m.out_features, "bias": m.bias is not None,
             "dtype": str(m.scales.dtype).replace("torch.", ""),
             "handle_outliers": bool(getattr(m, "handle_outliers", False)),

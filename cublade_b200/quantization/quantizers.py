@@ -122,8 +122,10 @@ QUANT_LAYER_REGISTRY = {}
 def _init_registry():
     if not QUANT_LAYER_REGISTRY:
         from .linear import cuBladeW8A16LinearLayer
+        from .linear_w4a16 import cuBladeW4A16LinearLayer
         from .linear_w8a8 import cuBladeW8A8LinearLayer
 
+        QUANT_LAYER_REGISTRY["w4a16"] = cuBladeW4A16LinearLayer  # reserved, not implemented, in the reference
         QUANT_LAYER_REGISTRY["w8a16"] = cuBladeW8A16LinearLayer
         QUANT_LAYER_REGISTRY["w8a8"] = cuBladeW8A8LinearLayer  # reserved, not implemented, in the reference
 

@@ -162,6 +162,28 @@ int32_t cb_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, i
                 int32_t out_kind, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------
+ * W4A16 linear: 4-bit symmetric weights (codes in [-7, 7], one scale per output feature), 16-bit activations,
+ * fp32 accumulation:   y[m, n] = T( (sum_k x[m, k] * code[n, k]) * scales[n] + bias[n] )
+ * The reference reserves the layer type "w4a16" (registry comment, cublade/quantization/quantizers.py:169-171)
+ * and has no kernel, layer or storage format for it.
+ * Packed weights wq4 [N, K / 2] bytes (K % 8 == 0): 32-bit word i of a row holds the codes k = 8i .. 8i + 7 as
+ * two's-complement nibbles, byte j = code(8i + j) | code(8i + 4 + j) << 4.
+ * cb_w4_quantize_rows: w [N, K] of dtype -> packed + scale_out [N] float32, the arithmetic of the reference's
+ *   per-channel INT8 quantizer (cublade/kernels/cuda/quantization/quantize_int8.cu:245-296) with qmax = 7.
+ * cb_w4_unpack: packed -> int8 codes [N, K].
+ * cb_w4a16_linear: M <= 16 with K % 128 == 0, N % 16 == 0 and 16-byte aligned rows streams the packed weights
+ *   once (no workspace); every other shape unpacks into `workspace` (cb_w4a16_workspace_bytes(M, N, K) bytes,
+ *   16-byte aligned) and runs the W8A16 path.  Too small a workspace -> CB_ERR_ARGUMENT.
+ * ------------------------------------------------------------------------ */
+int32_t cb_w4_quantize_rows(const void* w, int32_t dtype, int64_t N, int64_t K, float eps, void* packed, float* scale_out,
+                            void* stream);
+int32_t cb_w4_unpack(const void* packed, int64_t N, int64_t K, void* codes_int8, void* stream);
+size_t cb_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int32_t cb_w4a16_linear(const void* x, int32_t act_dtype, int64_t M, int64_t K, int64_t ldx, const void* wq4, int64_t N,
+                        const void* scales, int32_t scales_dtype, const void* bias, int32_t bias_dtype, void* y,
+                        int64_t ldy, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * W8A8 linear on the integer tensor cores (tcgen05 kind::i8, exact int32 accumulation):
  *   y[m, n] = T( (float(sum_k xq[m, k] * wq[n, k]) * x_scales[m]) * w_scales[n] + bias[n] )
  * The layer type the reference reserves as "w8a8" (cublade/quantization/quantizers.py:169-171) and does

@@ -280,3 +280,43 @@ def w8a16_forward_fp64(x: torch.Tensor, layer: dict, bias: Optional[torch.Tensor
     if bias is not None:
         y = y + bias.double()
     return y.reshape(*x.shape[:-1], q.shape[0])
+
+
+# ------------------------------------------------------------------------------------------------
+# W4A16 (layer type reserved by the reference's registry comment, cublade/quantization/quantizers.py:169-171,
+# without an implementation): the reference's symmetric per-channel arithmetic at qmax = 7.
+# ------------------------------------------------------------------------------------------------
+def int4_quantize_rows(x2d: torch.Tensor, eps: float = 1e-12):
+    """Rows of ``x2d [S, L]``: the INT8 row quantizer above (quantize_int8.cu:245-296, int8_pack.cuh:51-56) with
+    qmax = 7.  Returns (codes int8 [S, L] in [-7, 7], scale float32 [S])."""
+    x32 = x2d.detach().to("cpu").float()
+    amax = x32.abs().amax(dim=1) if x32.shape[1] else torch.zeros(x32.shape[0])
+    a = torch.maximum(amax, _f32(eps))
+    inv = (7.0 / a.double()).float()
+    scale = (1.0 / inv.double()).float()
+    q = torch.round(x32 * inv[:, None]).clamp_(-7, 7).to(torch.int8)
+    return q, scale
+
+
+def int4_pack(codes: torch.Tensor) -> torch.Tensor:
+    """int8 codes ``[N, K]`` (K % 8 == 0, values in [-8, 7]) -> uint8 ``[N, K // 2]``: byte ``4i + j`` of a row is
+    ``code[8i + j] & 15 | (code[8i + 4 + j] & 15) << 4``."""
+    n, k = codes.shape
+    c = (codes.to(torch.int16) & 15).view(n, k // 8, 2, 4)
+    return (c[:, :, 0, :] | (c[:, :, 1, :] << 4)).to(torch.uint8).reshape(n, k // 2)
+
+
+def int4_unpack(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``int4_pack``."""
+    n, half = packed.shape
+    b = packed.to(torch.int16).view(n, half // 4, 4)
+    lo, hi = b & 15, (b >> 4) & 15
+    c = torch.stack([lo, hi], dim=2).reshape(n, half * 2)
+    return torch.where(c >= 8, c - 16, c).to(torch.int8)
+
+
+def w4a16_quantize(weight: torch.Tensor, layer_dtype: torch.dtype):
+    """A layer dict for ``w8a16_forward`` (the forward is the W8A16 one on 4-bit codes) plus ``int4_weights``."""
+    q, s = int4_quantize_rows(weight.detach().to("cpu").contiguous())
+    return dict(int8_weights=q, int4_weights=int4_pack(q), scales=s.to(layer_dtype), scales_f32=s,
+                normal_cols=list(range(weight.shape[1])), outlier_cols=[], outlier_weights=None)

@@ -118,8 +118,8 @@ def test_replace_linear_layers_selection_and_bias_handling():
 def test_quantize_model_registry_errors_and_copy_semantics(monkeypatch):
     from cublade_b200.quantization import quantizers
 
-    with pytest.raises(ValueError, match="Unknown quant_type 'w4a16'. Available: w8a16, w8a8"):
-        cb.quantize_model(nn.Linear(4, 4), "w4a16")
+    with pytest.raises(ValueError, match="Unknown quant_type 'w2a16'. Available: w4a16, w8a16, w8a8"):
+        cb.quantize_model(nn.Linear(4, 4), "w2a16")
     monkeypatch.setitem(quantizers.QUANT_LAYER_REGISTRY, "w8a16", _Recorder)
     model = nn.Sequential(nn.Linear(4, 4))
     out = cb.quantize_model(model, "w8a16", inplace=False)

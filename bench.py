@@ -438,7 +438,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)  # launchers such as torchrun pin OMP_NUM_THREADS=1
-    if args.workload in ("w8a16", "w8a8"):
+    if args.workload in ("w8a16", "w8a8", "w4a16"):
         from cublade_b200 import workloads as W
         from oracle import oracle as O
 
@@ -446,7 +446,7 @@ def run_reference(args, rank, world):
         forward = O.w8a8_forward if a8 else O.w8a16_forward
         M = min(args.m, 64)
         w, x, _ = W.w8a16_case(M)
-        lay = O.w8a16_quantize(w, torch.bfloat16)
+        lay = O.w4a16_quantize(w, torch.bfloat16) if args.workload == "w4a16" else O.w8a16_quantize(w, torch.bfloat16)
         forward(x, lay)
         steps = max(1, min(args.steps, 5))
         t0 = time.perf_counter()
@@ -455,7 +455,8 @@ def run_reference(args, rank, world):
         dt = (time.perf_counter() - t0) / steps
         v = 2.0 * M * 14336 * 4096 / dt / 1e12
         sample = f"first {M} of {args.m} activation rows per step (reference CPU branch of the layer), {steps} steps"
-        metric = "W8A8 TOPS (2*M*N*K per step, activation quantization included)" if a8 else "W8A16 TFLOPS"
+        metric = ("W8A8 TOPS (2*M*N*K per step, activation quantization included)" if a8 else
+                  "W4A16 TFLOPS" if args.workload == "w4a16" else "W8A16 TFLOPS")
         print(json.dumps({"impl": "reference", "metric": metric, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
                           "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
                           "scaling": "strong", "vs_baseline": None, "dtype": "int8" if a8 else "bf16", "data": "synthetic",
@@ -503,14 +504,17 @@ def run_w8a16(args, rank, world, local_rank, device, dist):
     w, x_host, _ = W.w8a16_case(M)
     n0, n1 = shard_range(N_, rank, world)
     a8 = args.workload == "w8a8"  # int8 activations (quantized per token inside the step) on the integer tensor cores
-    layer_cls = cb.quantization.cuBladeW8A8LinearLayer if a8 else cb.cuBladeW8A16LinearLayer
+    a4 = args.workload == "w4a16"  # 4-bit weights: half the weight bytes; M > 16 unpacks to int8 and runs the W8A16 path
+    layer_cls = (cb.quantization.cuBladeW8A8LinearLayer if a8 else
+                 cb.quantization.cuBladeW4A16LinearLayer if a4 else cb.cuBladeW8A16LinearLayer)
     layer = layer_cls(K_, n1 - n0, bias=False, dtype=torch.bfloat16)
     layer.quantize(w[n0:n1].to(device))
     layer = layer.to(device)
     # HBM-bound shapes (M < 1024): the 58.7 MB of weights would stay in the 126 MB L2 between replays, so the
     # timed graph walks over `sets` copies of the layer (> 2x L2 in total) and every forward streams from HBM.
     tensor_bound = M >= 1024
-    sets = 1 if tensor_bound else max(2, -(-2 * 126_000_000 // ((n1 - n0) * K_)) + 1)
+    w_bytes = (n1 - n0) * K_ // (2 if a4 else 1)
+    sets = 1 if tensor_bound else max(2, -(-2 * 126_000_000 // w_bytes) + 1)
     layers = [layer]
     for _ in range(sets - 1):
         extra = layer_cls(K_, n1 - n0, bias=False, dtype=torch.bfloat16)
@@ -571,7 +575,7 @@ def run_w8a16(args, rank, world, local_rank, device, dist):
     flops = 2.0 * M * N_ * K_
     tf = flops / (ms * 1e-3) / 1e12
     local_tf = tf / world
-    bytes_local = (n1 - n0) * K_ + 2 * (n1 - n0) + 2 * M * K_ + 2 * M * (n1 - n0)
+    bytes_local = (n1 - n0) * K_ // (2 if a4 else 1) + 2 * (n1 - n0) + 2 * M * K_ + 2 * M * (n1 - n0)
     roof = ({"bound": "tensor", "achieved": local_tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
              "frac": local_tf / peaks["bf16_tflops_sustained"], "frac_of_burst_peak": local_tf / peaks["bf16_tflops"],
              "peak_note": "sustained cuBLAS bf16 figure: the kernel is timed back to back inside a long loop"}
@@ -580,25 +584,30 @@ def run_w8a16(args, rank, world, local_rank, device, dist):
              "frac": bytes_local / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
     roof.update({"kernel": "w8a16_tc_kernel (tcgen05/TMEM)" if M >= 17 else "w8a16_stream_kernel", "traffic": None,
                  "peak_source": peaks["source"], "avg_launch_us": ms * 1e3})
+    per_step = 2 if a8 else 1
+    if a4:
+        per_step = 1 if M <= 16 else 2
+        roof["kernel"] = "w4a16_stream_kernel" if M <= 16 else "w4_unpack_kernel + " + roof["kernel"]
     if a8:
         roof["kernel"] = "w8a8_tc_kernel (tcgen05 kind::i8) + per-token quantize_segments_kernel"
         roof["peak_note"] = ("measured cuBLAS bf16 figure; no int8 peak was measured on this pool, the integer path's "
                              "nominal rate is twice the bf16 one")
-    out = {"metric": "W8A8 TOPS (2*M*N*K per step, activation quantization included)" if a8 else "W8A16 TFLOPS", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": warmup,
+    out = {"metric": ("W8A8 TOPS (2*M*N*K per step, activation quantization included)" if a8 else
+                      "W4A16 TFLOPS" if a4 else "W8A16 TFLOPS"), "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": warmup,
            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
            "dtype": "int8" if a8 else "bf16", "data": "synthetic",
-           "config": {"workload": f"{args.workload}_linear M={M} N={N_} K={K_} int8 per-output-channel weights, bf16 activations"
+           "config": {"workload": f"{args.workload}_linear M={M} N={N_} K={K_} {'int4' if a4 else 'int8'} per-output-channel weights, bf16 activations"
                                   + (" quantized per token to int8 in the step" if a8 else ""),
                       "l2_policy": "back-to-back replays; weights (58.7 MB) + activations stay L2-resident, the shape is "
                                    "tensor-bound" if tensor_bound else
                                    f"each step streams its weights from HBM: the graph walks over {sets} copies of the layer "
-                                   f"({sets * (n1 - n0) * K_ / 1e6:.0f} MB of int8 weights, L2 is 126 MB)",
+                                   f"({sets * w_bytes / 1e6:.0f} MB of quantized weights, L2 is 126 MB)",
                       "launch": "one CUDA graph per step" if sets == 1 else f"one CUDA graph per {sets} steps", "seed": 3, "sharding": f"output features over {world} rank(s)"},
            "clocks": clocks.summary(),
            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K_ * 2,
                    "d2h_bytes_per_step": M * (n1 - n0) * 2, "ms_per_step": e2e_ms, "steps": steps_e2e},
-           "gpu_launches": K * (2 if a8 else 1),
-           "gpu_launches_note": f"{2 if a8 else 1} kernel(s) of libcublade_b200.so per step, replayed from a CUDA graph",
+           "gpu_launches": K * per_step,
+           "gpu_launches_note": f"{per_step} kernel(s) of libcublade_b200.so per step, replayed from a CUDA graph",
            "roofline": roof}
     if not args.no_cpu_baseline and a8:
         from oracle import oracle as O
@@ -656,7 +665,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS) + ["w8a16", "w8a8"])
+    ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS) + ["w8a16", "w8a8", "w4a16"])
     ap.add_argument("--m", type=int, default=2048, help="activation rows for --workload w8a16")
     ap.add_argument("--impl", default="cublade_b200", choices=["cublade_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -684,7 +693,7 @@ def main():
     from cublade_b200 import _native as N
 
     N.lib()  # fail loudly if the extension is missing
-    if args.workload in ("w8a16", "w8a8"):
+    if args.workload in ("w8a16", "w8a8", "w4a16"):
         run_w8a16(args, rank, world, local_rank, device, dist)
         if dist is not None:
             dist.barrier()

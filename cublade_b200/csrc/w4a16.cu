@@ -150,7 +150,9 @@ struct W4Params {
 // of each activation row.  Requires K % 128 == 0, N % 16 == 0, 16-byte aligned rows.
 template <typename A, int MT>
 __global__ void __launch_bounds__(kWarps * 32, 7) w4a16_stream_kernel(const W4Params p) {
-    constexpr int U = 2;  // rounds per pipeline stage: 64 bytes of weights per thread in flight
+    // rounds per pipeline stage: 64 bytes of weights per thread in flight; one round with two activation tiles,
+    // whose second accumulator set would otherwise spill under the 72-register cap of seven CTAs per SM
+    constexpr int U = MT == 1 ? 2 : 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int64_t n0 = (int64_t)blockIdx.x * 16;

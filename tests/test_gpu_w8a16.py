@@ -188,7 +188,7 @@ def test_quantize_model_toy_mlp_thresholds():
     assert isinstance(q_sel.fc1, nn.Linear) and isinstance(q_sel.fc3, nn.Linear)
     assert isinstance(q_sel.fc2, cb.cuBladeW8A16LinearLayer)
     with pytest.raises(ValueError, match="Unknown quant_type"):
-        cb.quantize_model(Toy(), "w4a16")
+        cb.quantize_model(Toy(), "w2a16")
 
 
 def test_checkpoint_round_trip_reproduces_the_forward_bit_for_bit(tmp_path):

@@ -106,7 +106,11 @@ struct Cfg {
     // "full" barrier (TMA bytes + the eight converter warps) and one "empty" barrier (one tcgen05.commit) per
     // stage -- the MMA thread's loop is the critical path of the kernel, and every barrier it probes or
     // commits to costs it time the tensor core spends idle.
-    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 3 : (MODE == kTmemA128 ? 8 : 12));  // kTmemA: three 32-column A stages fit
+    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 6 : (MODE == kTmemA128 ? 8 : 12));
+    // kTmemA: only three 32-column A stages fit beside two 208-column accumulators, but shared memory holds six
+    // activation + int8 stages: ring slot s uses tensor-memory A stage s % 3, and a converter waits, besides the int8
+    // tile, for the MMAs of the k-block three slots back (the `empty` barrier of that slot) before it overwrites the stage.
+    static constexpr int kTmemAStages = MODE == kTmemA ? 3 : kStages;
     // kTmemA128 has TWO MMA issuers: a thread needs ~350 cycles to issue the four MMAs of a k-block and commit
     // them, whatever their size, so with short activation tiles one issuer, not the tensor core, sets the pace.
     // Issuer i takes the k-blocks of parity i of a work item and accumulates into accumulator i; the epilogue adds
@@ -118,8 +122,8 @@ struct Cfg {
     // eight converter warps working on the SAME k-block that chain, not the memory system, paced the kernel
     // (timing floors: no change with 8 or 128 weight rows per TMA box, 12 instead of 8 stages, or no MMAs).
     // The third group are the epilogue warps, idle during a tile's main loop in these modes.
-    static constexpr int kConvGroups = 3;
-    static constexpr int kFullArrivals = kDual ? 1 + 4 : 1 + kConvWarps;  // TMA expect_tx + converter warps per stage
+    static constexpr int kConvGroups = kDual ? 3 : 2;  // kTmemA: the two groups of converter warps
+    static constexpr int kFullArrivals = MODE == kSmemA ? 1 + kConvWarps : 1 + 4;  // TMA expect_tx + converter warps per stage
     static constexpr int kStagesX = kStages;
     static constexpr int kStagesA = kStages;
     static constexpr int kStagesW8 = kStages;                      // int8 weight tiles (8 KiB each), part of the same ring
@@ -139,7 +143,7 @@ struct Cfg {
     static constexpr uint32_t abort_flag = tmem_slot + 4;
     static constexpr uint32_t total = abort_flag + 4;
     static constexpr uint32_t kSmemBytes = total + 1024;  // + slack to align the base to 1024 B
-    static_assert(kACol + kStagesA * kAColsPerStage <= kTmemCols || MODE == kSmemA, "tensor memory map");
+    static_assert(kACol + kTmemAStages * kAColsPerStage <= kTmemCols || MODE == kSmemA, "tensor memory map");
     static_assert(kSmemBytes <= 232448, "shared memory map");
 };
 
@@ -323,8 +327,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // kDual modes: widen the k-blocks of work item w that belong to converter group `group` (every kConvGroups-th
-    // k-block of the CTA's running count) into their tensor-memory stages.  State of the calling warp: ring stage,
+    // Tensor-memory modes: widen the k-blocks of work item w that belong to converter group `group` (every
+    // kConvGroups-th k-block of the CTA's running count) into their tensor-memory stages.  A thread owns weight row
+    // 32 * quarter + lane = its tensor-memory lane; the int8 tile arrived with the 64-byte TMA swizzle, so the eight
+    // lanes of a quarter-warp hit eight different bank groups.  State of the calling warp: ring stage,
     // phase and the running count modulo kConvGroups.  Returns false when a wait gave up.
     uint32_t cv_s = 0, cv_ph = 0, cv_g = 0;
     auto convert_item_tmem = [&](const WorkItem& w, uint32_t group) -> bool {
@@ -335,8 +341,17 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (cv_g == group) {
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(full_w8 + 8 * cv_s, cv_ph, abort_flag) ? 1 : 0;
+                if constexpr (C::kTmemAStages != C::kStages) {
+                    // the tensor-memory stage is shared with the slot kTmemAStages back: its MMAs must have retired
+                    // (same ring round for the upper slots, the round before for the lower ones)
+                    if (lane == 0 && okw) {
+                        const uint32_t back = cv_s >= (uint32_t)C::kTmemAStages ? cv_s - C::kTmemAStages : cv_s + C::kTmemAStages;
+                        okw = mbar_wait(empty_a + 8 * back, cv_s >= (uint32_t)C::kTmemAStages ? cv_ph : cv_ph ^ 1u, abort_flag) ? 1 : 0;
+                    }
+                }
                 if (__shfl_sync(0xffffffffu, okw, 0) == 0) return false;
                 tc_fence_after();
+                const uint32_t a_stage = C::kTmemAStages == C::kStages ? cv_s : cv_s % (uint32_t)C::kTmemAStages;
                 const uint32_t rbase = sw8 + cv_s * kBytesW8 + (uint32_t)(row * 64);
 #pragma unroll
                 for (int khalf = 0; khalf < 2; ++khalf) {
@@ -350,7 +365,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 8; ++j) CB_WIDEN<A>::four(c[j], o[2 * j], o[2 * j + 1]);
                     tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                                  (uint32_t)(C::kACol + cv_s * C::kAColsPerStage + khalf * 16), o);
+                                  (uint32_t)(C::kACol + a_stage * C::kAColsPerStage + khalf * 16), o);
                 }
                 tmem_st_wait();
                 tc_fence_before();
@@ -485,7 +500,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                                      (kb > kb_first || k > 0) ? 1u : 0u);
                         }
                     } else {
-                        const uint32_t a_tmem = tmem_base + C::kACol + s_a * C::kAColsPerStage;
+                        const uint32_t a_tmem = tmem_base + C::kACol + (s_a % (uint32_t)C::kTmemAStages) * C::kAColsPerStage;
 #pragma unroll
                         for (int k = 0; k < kBlockK / 16; ++k) {
                             // 16 k = 8 columns of A, 32 bytes of every B row
@@ -601,7 +616,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         bool ok = true;
         RP_DECL
         WorkItem w;
-        if constexpr (C::kDual) {
+        if constexpr (MODE != kSmemA) {
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) ok = convert_item_tmem(w, (uint32_t)(cw >> 2));
         } else
         for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
@@ -651,28 +666,6 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                                      : "memory");
                     }
                     fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
-                } else {
-                    // This thread owns weight row (32 * quarter + lane) = its tensor-memory lane and half of
-                    // the 64 k: warps 6..9 take k 0..31, warps 10..13 k 32..63.  The int8 tile arrived with
-                    // the 64-byte TMA swizzle (16-byte chunk c of row r sits at c ^ ((r >> 1) & 3)), so the
-                    // eight lanes of a quarter-warp hit eight different bank groups.
-                    const int quarter = warp & 3, khalf = cw >> 2;
-                    const int row = quarter * 32 + lane;
-                    const uint32_t rbase = src + (uint32_t)(row * 64);
-                    const uint32_t sw = (uint32_t)((row >> 1) & 3);
-                    uint32_t c[8];
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(c[4 * j]), "=r"(c[4 * j + 1]), "=r"(c[4 * j + 2]), "=r"(c[4 * j + 3])
-                                     : "r"(rbase + ((((uint32_t)(2 * khalf + j)) ^ sw) << 4)));
-                    uint32_t o[16];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) CB_WIDEN<A>::four(c[j], o[2 * j], o[2 * j + 1]);
-                    tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                                  (uint32_t)(C::kACol + s_a * C::kAColsPerStage + khalf * 16), o);
-                    tmem_st_wait();
-                    tc_fence_before();
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a + 8 * s_a);
@@ -813,26 +806,32 @@ static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, i
 }
 
 // Operand-A mode and tile height (a multiple of 16 rows) with the shortest modelled schedule.
-// Mode: measured on B200 (N = 14336, K = 4096) the tensor-memory route is 7-10 % ahead while one
-// activation tile of <= 208 rows covers M, and behind from there on (its tiles are 208 rows, not 256).
 static TcPlan make_plan(int64_t M, int64_t N, int64_t K, int sms, bool may_split) {
-    int mode = M <= Cfg<kTmemA64>::kMaxTileX    ? kTmemA64
-               : M <= Cfg<kTmemA128>::kMaxTileX ? kTmemA128
-               : M <= Cfg<kTmemA>::kMaxTileX    ? kTmemA
-                                                : kSmemA;
+    // M <= 128: one short tile per CTA, the deep-ring modes.  Above: shared-memory A (tiles up to 256 rows) against
+    // tensor-memory A (up to 208 rows), whichever models shorter -- measured on B200 (N = 14336, K = 4096) the
+    // tensor-memory route needs ~9 % less time per k-block and row (M = 416: 65 vs 71 us, M = 1024: 118 vs 134 us),
+    // which its smaller tiles give back when they cost an extra round (M = 4096: 446 vs 430 us).
+    int modes[2] = {kSmemA, kTmemA};
+    int n_modes = 2;
+    if (M <= Cfg<kTmemA64>::kMaxTileX) { modes[0] = kTmemA64; n_modes = 1; }
+    else if (M <= Cfg<kTmemA128>::kMaxTileX) { modes[0] = kTmemA128; n_modes = 1; }
 #ifdef CB_TC_DEVTOOLS
-    if (const char* f = getenv("CB_TC_MODE")) mode = atoi(f);
+    if (const char* f = getenv("CB_TC_MODE")) { modes[0] = atoi(f); n_modes = 1; }
 #endif
     TcPlan best{};
     double best_cost = 1e300;
-    const int max_tx = mode == kSmemA ? Cfg<kSmemA>::kMaxTileX
-                       : mode == kTmemA  ? Cfg<kTmemA>::kMaxTileX
-                       : mode == kTmemA128 ? Cfg<kTmemA128>::kMaxTileX
-                                           : Cfg<kTmemA64>::kMaxTileX;
-    for (int tx = max_tx; tx >= 32; tx -= 16) {
-        double cost;
-        const TcPlan pl = plan_for_tile(mode, tx, M, N, K, sms, may_split, &cost);
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = pl; }
+    for (int i = 0; i < n_modes; ++i) {
+        const int mode = modes[i];
+        const int max_tx = mode == kSmemA ? Cfg<kSmemA>::kMaxTileX
+                           : mode == kTmemA  ? Cfg<kTmemA>::kMaxTileX
+                           : mode == kTmemA128 ? Cfg<kTmemA128>::kMaxTileX
+                                               : Cfg<kTmemA64>::kMaxTileX;
+        for (int tx = max_tx; tx >= 32; tx -= 16) {
+            double cost;
+            const TcPlan pl = plan_for_tile(mode, tx, M, N, K, sms, may_split, &cost);
+            if (mode == kTmemA) cost *= 0.91;
+            if (cost < best_cost - 1e-9) { best_cost = cost; best = pl; }
+        }
     }
     return best;
 }

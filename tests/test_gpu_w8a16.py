@@ -53,7 +53,7 @@ def test_config4_shapes_bf16(M):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K,bias", [(1, 64, 64, False), (3, 40, 128, True), (16, 256, 1024, True),
                                         (33, 130, 320, True), (70, 512, 4096, False), (256, 384, 512, True),
-                                        (5, 24, 72, True), (9, 17, 100, False), (130, 1000, 968, True)])
+                                        (5, 24, 72, True), (9, 17, 100, False), (130, 1000, 968, True), (200, 640, 4096, True)])
 def test_small_shapes_both_paths(M, N, K, bias, dtype, path):
     from cublade_b200.bindings.w8a16 import w8a16_linear
 

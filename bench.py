@@ -666,7 +666,9 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="int8_channel", choices=sorted(WORKLOADS) + ["w8a16", "w8a8", "w4a16"])
-    ap.add_argument("--m", type=int, default=2048, help="activation rows for --workload w8a16")
+    ap.add_argument("--m", "--rows", dest="m", type=int, default=2048,
+                    help="activation rows for the linear workloads (spell it --rows under torchrun, whose own parser "
+                         "rejects --m as an ambiguous abbreviation)")
     ap.add_argument("--impl", default="cublade_b200", choices=["cublade_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-w8a16", action="store_true", help="skip the W8A16 TFLOP/s table")

@@ -220,3 +220,22 @@ def test_checkpoint_round_trip_reproduces_the_forward_bit_for_bit(tmp_path):
         part = load_quantized_model(make(), path, rank=r, world_size=2).cuda()
         lo, hi = shard_range(512, r, 2)
         assert torch.equal(part[0](x).view(torch.int16), h[:, lo:hi].contiguous().view(torch.int16))
+
+
+@pytest.mark.parametrize("M,N,K", [(48, 19200, 512), (100, 19200 + 128, 576), (24, 40000, 256), (200, 19200, 448),
+                                   (500, 9600, 512)])
+def test_more_tiles_than_sms(M, N, K):
+    """Persistent schedule with several tiles per CTA in every operand mode of the tensor-core kernel: the short-tile
+    modes (two MMA issuers, the epilogue warps converting during the next tile's main loop), the six-slot
+    tensor-memory mode and the shared-memory mode, with a ragged last round and a ragged last tile."""
+    from cublade_b200 import _native as Nat
+    from cublade_b200.bindings.w8a16 import w8a16_linear
+
+    g = torch.Generator().manual_seed(M + N + K)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    b = torch.randn(N, generator=g).to(torch.bfloat16)
+    lay = O.w8a16_quantize(w, torch.bfloat16)
+    y = w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda(), path=3)
+    _check(y, O.w8a16_forward(x, lay, b), f"M={M} N={N} K={K}")
+    assert Nat.device_error_state() == 0

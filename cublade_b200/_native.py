@@ -67,6 +67,8 @@ SIGNATURES = {
     "cb_rmsnorm_quantize": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_float, c_float, c_int32, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_gather_columns": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p]),
+    "cb_gather_columns_padded": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64,
+                                           c_int32, c_void_p]),
 }
 
 _lib = None

@@ -20,19 +20,24 @@ def _check_2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be 2-D with unit inner stride")
 
 
-def gather_columns(src: torch.Tensor, cols: torch.Tensor, ld_dst: Optional[int] = None) -> torch.Tensor:
+def gather_columns(src: torch.Tensor, cols: torch.Tensor, ld_dst: Optional[int] = None,
+                   pad_to: Optional[int] = None) -> torch.Tensor:
     """``src[:, cols]`` for a 2-D CUDA tensor of a 2- or 4-byte dtype; the result's row stride is
-    ``ld_dst`` elements (default: the column count rounded up to a multiple of 8)."""
+    ``ld_dst`` elements (default: the column count rounded up to a multiple of 8).  With ``pad_to``
+    the result has ``pad_to`` columns, the ones behind ``len(cols)`` zero."""
     _check_2d(src, "src")
     if not src.is_cuda or not cols.is_cuda or cols.dtype != torch.int64:
         raise ValueError("gather_columns: src and cols (int64) must be CUDA tensors")
     M, n = src.shape[0], cols.numel()
-    ld = ld_dst if ld_dst is not None else (n + 7) // 8 * 8
+    width = n if pad_to is None else int(pad_to)
+    if width < n:
+        raise ValueError("gather_columns: pad_to is smaller than the number of columns")
+    ld = ld_dst if ld_dst is not None else (width + 7) // 8 * 8
     with N.device_guard(src):
         buf = torch.empty((M, max(ld, 1)), dtype=src.dtype, device=src.device)
-        N.check(N.lib().cb_gather_columns(src.data_ptr(), M, src.stride(0), cols.data_ptr(), n, buf.data_ptr(),
-                                          buf.stride(0), src.element_size(), N.stream_ptr(src)))
-    return buf[:, :n]
+        N.check(N.lib().cb_gather_columns_padded(src.data_ptr(), M, src.stride(0), cols.data_ptr(), n, width,
+                                                 buf.data_ptr(), buf.stride(0), src.element_size(), N.stream_ptr(src)))
+    return buf[:, :width]
 
 
 def w8a16_linear(

@@ -8,7 +8,6 @@ Python dependency; the CUDA runtime is linked statically.
 """
 from __future__ import annotations
 
-import os
 import shutil
 import subprocess
 import sys
@@ -54,7 +53,6 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     for src in sources:
         obj = OBJ / (src.stem + ".o")
         flags = [f for f in NVCC_FLAGS if not (src.name in FMAD_OK and f == "-fmad=false")]
-        flags += os.environ.get("CB_EXTRA_NVCC_FLAGS", "").split()
         # an object built with other flags is stale too: the flags it was built with sit beside it
         stamp = obj.with_suffix(".flags")
         same_flags = stamp.exists() and stamp.read_text() == " ".join(flags)

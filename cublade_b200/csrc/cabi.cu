@@ -28,6 +28,15 @@ int32_t cuda_result(cudaError_t e, const char* what, int launches) {
     return CB_OK;
 }
 
+}  // namespace
+
+namespace cb {
+// entry points that live in other translation units account for their launches here
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+}  // namespace cb
+
+namespace {
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool is_half_like(int32_t dt) { return dt == CB_F16 || dt == CB_BF16; }
 inline bool is_float_like(int32_t dt) { return dt == CB_F16 || dt == CB_BF16 || dt == CB_F32; }
@@ -205,8 +214,21 @@ int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int6
     if (elem_size != 2 && elem_size != 4) return fail(CB_ERR_ARGUMENT, "cb_gather_columns: elem_size must be 2 or 4");
     if (M == 0 || ncols == 0) return CB_OK;
     if (!src || !cols || !dst) return fail(CB_ERR_ARGUMENT, "cb_gather_columns: null pointer");
-    return cuda_result(cb::launch_gather_cols(src, M, ld_src, cols, ncols, dst, ld_dst, elem_size, as_stream(stream)),
+    return cuda_result(cb::launch_gather_cols(src, M, ld_src, cols, ncols, ncols, dst, ld_dst, elem_size,
+                                              as_stream(stream)),
                        "cb_gather_columns", 1);
+}
+
+int32_t cb_gather_columns_padded(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
+                                 int64_t ncols_padded, void* dst, int64_t ld_dst, int32_t elem_size, void* stream) {
+    if (M < 0 || ncols < 0 || ncols_padded < ncols || ld_dst < ncols_padded)
+        return fail(CB_ERR_ARGUMENT, "cb_gather_columns_padded: need 0 <= ncols <= ncols_padded <= ld_dst");
+    if (elem_size != 2 && elem_size != 4) return fail(CB_ERR_ARGUMENT, "cb_gather_columns_padded: elem_size must be 2 or 4");
+    if (M == 0 || ncols_padded == 0) return CB_OK;
+    if (!src || (ncols > 0 && !cols) || !dst) return fail(CB_ERR_ARGUMENT, "cb_gather_columns_padded: null pointer");
+    return cuda_result(cb::launch_gather_cols(src, M, ld_src, cols, ncols, ncols_padded, dst, ld_dst, elem_size,
+                                              as_stream(stream)),
+                       "cb_gather_columns_padded", 1);
 }
 
 size_t cb_gemm_workspace_bytes(int64_t N, int64_t K, int32_t in_kind) {

@@ -125,8 +125,11 @@ cudaError_t launch_tc_gemm(const void* a, const void* b, int64_t M, int64_t N, i
 // reads (and leaves untouched) the per-device flag a kernel raises when one of its bounded waits
 // expired; synchronises the stream.
 cudaError_t w8a16_tc_read_error(unsigned int* host_value, cudaStream_t s);
-// gathers columns: dst[m, j] = src[m, cols[j]] (activation re-pack for the outlier split)
+// gathers columns: dst[m, j] = src[m, cols[j]] for j < ncols and 0 for ncols <= j < ncols_padded
+// (activation re-pack for the outlier split; the zero columns pad K to what the tensor-core kernels load)
 cudaError_t launch_gather_cols(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
-                               void* dst, int64_t ld_dst, int elem_size, cudaStream_t s);
+                               int64_t ncols_padded, void* dst, int64_t ld_dst, int elem_size, cudaStream_t s);
+// adds n to the library's launch counter (cb_launch_count)
+void count_launches(int n);
 
 }  // namespace cb

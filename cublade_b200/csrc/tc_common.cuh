@@ -236,6 +236,17 @@ struct Widen<__half> {
     __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
 };
 
+// v rounded to the activation type A and widened back.  The reference's forward materialises a
+// 16-bit tensor after every step -- the GEMM's output, the product with the scales (themselves cast
+// to the activation type), the sum with the outlier product, the sum with the bias
+// (cublade/quantization/linear.py:97-135) -- so an epilogue that reproduces its results bit for bit
+// (up to the order of the fp32 accumulation) rounds in the same places:
+//   v = r(r(acc) * r(scale));  v = r(v + r(side));  v = r(v + r(bias))
+template <typename A>
+__device__ __forceinline__ float ref_round(float v) {
+    return Widen<A>::to_float(Widen<A>::from_float(v));
+}
+
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
     if (dtype == kF32) return static_cast<const float*>(p)[i];
     if (dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);

@@ -33,6 +33,7 @@ constexpr size_t kScratchBytes = 16u << 20;
 static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 unsigned char* scratch_for_current_device(cudaError_t* err) {
+    // one slot per device; two host threads that fill a slot at the same time store the same address
     static unsigned char* cached[64] = {nullptr};
     int dev = 0;
     *err = cudaGetDevice(&dev);
@@ -70,15 +71,24 @@ int32_t cb_w8a16_linear_outlier_static(const void* x, int64_t M, int64_t K, int6
     };
     if (act_dtype != CB_F16 && act_dtype != CB_BF16)
         return fail(CB_ERR_DTYPE, "cb_w8a16_linear_outlier_static: activations must be float16 or bfloat16");
+    auto float_like = [](int32_t dt) { return dt == CB_F16 || dt == CB_BF16 || dt == CB_F32; };
+    if (!float_like(scales_dtype))
+        return fail(CB_ERR_DTYPE, "cb_w8a16_linear_outlier_static: bad scales dtype");
+    if (bias && !float_like(bias_dtype))
+        return fail(CB_ERR_DTYPE, "cb_w8a16_linear_outlier_static: bad bias dtype");
     if (M < 0 || N < 0 || K < 0 || KO < 0 || KO > K)
         return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear_outlier_static: bad sizes");
     if (M == 0 || N == 0) return CB_OK;
+    if (ldx < K || ldy < N)
+        return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear_outlier_static: row stride too small (need ldx >= K, ldy >= N)");
     if (!x || !wq || !scales || !y || (K - KO > 0 && !normal_cols) || (KO > 0 && (!outlier_cols || !wo)))
         return fail(CB_ERR_ARGUMENT, "cb_w8a16_linear_outlier_static: null pointer");
     const int64_t kn = K - KO;
     const int64_t ld_n = (kn + 7) / 8 * 8, ld_o = (KO + 7) / 8 * 8;
-    const size_t need = (size_t)M * (size_t)(ld_n + ld_o) * 2u;
-    if (need > kScratchBytes) {
+    // compared in divided form: M * (ld_n + ld_o) * 2 cannot wrap for any int64 sizes this way
+    const bool fits = ld_n + ld_o == 0 || (uint64_t)M <= (uint64_t)(kScratchBytes / 2u) / (uint64_t)(ld_n + ld_o);
+    const size_t need = fits ? (size_t)M * (size_t)(ld_n + ld_o) * 2u : ~(size_t)0;
+    if (!fits) {
         snprintf(g_static_err, sizeof(g_static_err),
                  "cb_w8a16_linear_outlier_static: needs %zu bytes of scratch, the built-in scratch holds %zu "
                  "(M * (K rounded up per column set) * 2 must not exceed it); use cb_w8a16_linear with your own buffers",
@@ -95,13 +105,16 @@ int32_t cb_w8a16_linear_outlier_static(const void* x, int64_t M, int64_t K, int6
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     void* xn = scratch;                                   // [M, ld_n]
     void* xo = scratch + (size_t)M * (size_t)ld_n * 2u;   // [M, ld_o]   (offset is a multiple of 16 bytes)
+    int launches = 1;
     if (kn > 0) {
-        e = cb::launch_gather_cols(x, M, ldx, normal_cols, kn, xn, ld_n, 2, s);
+        e = cb::launch_gather_cols(x, M, ldx, normal_cols, kn, kn, xn, ld_n, 2, s);
         if (e != cudaSuccess) return fail(CB_ERR_CUDA, cudaGetErrorString(e));
+        ++launches;
     }
     if (KO > 0) {
-        e = cb::launch_gather_cols(x, M, ldx, outlier_cols, KO, xo, ld_o, 2, s);
+        e = cb::launch_gather_cols(x, M, ldx, outlier_cols, KO, KO, xo, ld_o, 2, s);
         if (e != cudaSuccess) return fail(CB_ERR_CUDA, cudaGetErrorString(e));
+        ++launches;
     }
     cb::W8A16Args a;
     a.x = xn; a.M = M; a.K = kn; a.ldx = ld_n;
@@ -117,6 +130,7 @@ int32_t cb_w8a16_linear_outlier_static(const void* x, int64_t M, int64_t K, int6
     a.workspace_bytes = used < kScratchBytes ? kScratchBytes - used : 0;
     e = cb::launch_w8a16(a, 0, s);
     if (e != cudaSuccess) return fail(CB_ERR_CUDA, cudaGetErrorString(e));
+    cb::count_launches(launches);
     return CB_OK;
 }
 

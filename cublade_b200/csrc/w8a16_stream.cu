@@ -82,6 +82,13 @@ struct Act<__half> {
     __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
 };
 
+// v rounded to the activation type and widened back: the epilogues below round where the reference's
+// forward materialises a 16-bit tensor (after the GEMM, after the scales, after adding the outlier
+// product, after the bias; cublade/quantization/linear.py:97-135), so results agree with it bit for
+// bit up to the order of the fp32 accumulation.
+template <typename A>
+__device__ __forceinline__ float ref_round(float v) { return Act<A>::to_float(Act<A>::from_float(v)); }
+
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
     if (dtype == kF32) return static_cast<const float*>(p)[i];
     if (dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
@@ -259,36 +266,6 @@ __global__ void __launch_bounds__(kWarps * 32) w8a16_stream_kernel(const StreamP
         }
     }
 
-    // per-row scale (rows g and g+8 of this tile)
-    const float s0 = r0_ok ? load_as_float(p.scales, p.scales_dtype, n0 + g) : 0.0f;
-    const float s1 = r1_ok ? load_as_float(p.scales, p.scales_dtype, n0 + g + 8) : 0.0f;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        acc[mt][0] *= s0; acc[mt][1] *= s0;
-        acc[mt][2] *= s1; acc[mt][3] *= s1;
-    }
-
-    // 16-bit side product over the outlier columns, k16-steps dealt round-robin to the warps
-    if (p.KO > 0) {
-        const A* xo = static_cast<const A*>(p.xo);
-        const A* wo = static_cast<const A*>(p.wo);
-        const int64_t osteps = (p.KO + 15) / 16;
-        for (int64_t st = warp; st < osteps; st += kWarps) {
-            const int64_t k = st * 16 + t * 4;
-            uint32_t a0[2], a1[2];
-            load_acts<A, 1>(wo + (n0 + g) * p.KO, k, p.KO, r0_ok, a0);
-            load_acts<A, 1>(wo + (n0 + g + 8) * p.KO, k, p.KO, r1_ok, a1);
-            const uint32_t a[4] = {a0[0], a1[0], a0[1], a1[1]};
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const int64_t m = p.m0 + mt * 8 + g;
-                uint32_t b[2];
-                load_acts<A, 1>(xo + m * p.ldxo, k, p.KO, m < p.M, b);
-                Act<A>::mma(acc[mt], a, b[0], b[1]);
-            }
-        }
-    }
-
     // cross-warp reduction of the K split
     __shared__ float red[kWarps - 1][MT * 4][32];
     if (warp > 0) {
@@ -306,18 +283,59 @@ __global__ void __launch_bounds__(kWarps * 32) w8a16_stream_kernel(const StreamP
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[mt][j] += red[w][mt * 4 + j][lane];
 
+    // GEMM output and its product with the per-row scale (rows g and g+8 of this tile), each rounded
+    // to the activation type as in the reference
+    const float s0 = r0_ok ? ref_round<A>(load_as_float(p.scales, p.scales_dtype, n0 + g)) : 0.0f;
+    const float s1 = r1_ok ? ref_round<A>(load_as_float(p.scales, p.scales_dtype, n0 + g + 8)) : 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        acc[mt][0] = ref_round<A>(ref_round<A>(acc[mt][0]) * s0); acc[mt][1] = ref_round<A>(ref_round<A>(acc[mt][1]) * s0);
+        acc[mt][2] = ref_round<A>(ref_round<A>(acc[mt][2]) * s1); acc[mt][3] = ref_round<A>(ref_round<A>(acc[mt][3]) * s1);
+    }
+
+    // 16-bit side product over the outlier columns (few: this warp alone), rounded, then added
+    if (p.KO > 0) {
+        const A* xo = static_cast<const A*>(p.xo);
+        const A* wo = static_cast<const A*>(p.wo);
+        float side[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) side[mt][j] = 0.0f;
+        const int64_t osteps = (p.KO + 15) / 16;
+        for (int64_t st = 0; st < osteps; ++st) {
+            const int64_t k = st * 16 + t * 4;
+            uint32_t a0[2], a1[2];
+            load_acts<A, 1>(wo + (n0 + g) * p.KO, k, p.KO, r0_ok, a0);
+            load_acts<A, 1>(wo + (n0 + g + 8) * p.KO, k, p.KO, r1_ok, a1);
+            const uint32_t a[4] = {a0[0], a1[0], a0[1], a1[1]};
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int64_t m = p.m0 + mt * 8 + g;
+                uint32_t b[2];
+                load_acts<A, 1>(xo + m * p.ldxo, k, p.KO, m < p.M, b);
+                Act<A>::mma(side[mt], a, b[0], b[1]);
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[mt][j] = ref_round<A>(acc[mt][j] + ref_round<A>(side[mt][j]));
+    }
+
     // D fragment: acc[mt][0..1] -> (row g, m = 2t, 2t+1), acc[mt][2..3] -> (row g+8, same m)
     A* y = static_cast<A*>(p.y);
-    const float b0 = (p.bias && r0_ok) ? load_as_float(p.bias, p.bias_dtype, n0 + g) : 0.0f;
-    const float b1 = (p.bias && r1_ok) ? load_as_float(p.bias, p.bias_dtype, n0 + g + 8) : 0.0f;
+    const bool has_bias = p.bias != nullptr;
+    const float b0 = (has_bias && r0_ok) ? ref_round<A>(load_as_float(p.bias, p.bias_dtype, n0 + g)) : 0.0f;
+    const float b1 = (has_bias && r1_ok) ? ref_round<A>(load_as_float(p.bias, p.bias_dtype, n0 + g + 8)) : 0.0f;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int64_t m = p.m0 + mt * 8 + 2 * t + j;
             if (m >= p.M) continue;
-            if (r0_ok) y[m * p.ldy + n0 + g] = Act<A>::from_float(acc[mt][j] + b0);
-            if (r1_ok) y[m * p.ldy + n0 + g + 8] = Act<A>::from_float(acc[mt][2 + j] + b1);
+            if (r0_ok) y[m * p.ldy + n0 + g] = Act<A>::from_float(has_bias ? acc[mt][j] + b0 : acc[mt][j]);
+            if (r1_ok) y[m * p.ldy + n0 + g + 8] = Act<A>::from_float(has_bias ? acc[mt][2 + j] + b1 : acc[mt][2 + j]);
         }
     }
 }
@@ -419,32 +437,6 @@ __global__ void __launch_bounds__(kWarps * 32, 7) w8a16_stream_fast_kernel(const
         }
     }
 
-    const float s0 = load_as_float(p.scales, p.scales_dtype, n0 + g);
-    const float s1 = load_as_float(p.scales, p.scales_dtype, n0 + g + 8);
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        acc[mt][0] *= s0; acc[mt][1] *= s0;
-        acc[mt][2] *= s1; acc[mt][3] *= s1;
-    }
-    if (p.KO > 0) {
-        const A* xo = static_cast<const A*>(p.xo);
-        const A* wo = static_cast<const A*>(p.wo);
-        const int64_t osteps = (p.KO + 15) / 16;
-        for (int64_t st = warp; st < osteps; st += kWarps) {
-            const int64_t k = st * 16 + t * 4;
-            uint32_t a0[2], a1[2];
-            load_acts<A, 1>(wo + (n0 + g) * p.KO, k, p.KO, true, a0);
-            load_acts<A, 1>(wo + (n0 + g + 8) * p.KO, k, p.KO, true, a1);
-            const uint32_t a[4] = {a0[0], a1[0], a0[1], a1[1]};
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const int64_t m = p.m0 + mt * 8 + g;
-                uint32_t b[2];
-                load_acts<A, 1>(xo + m * p.ldxo, k, p.KO, m < p.M, b);
-                Act<A>::mma(acc[mt], a, b[0], b[1]);
-            }
-        }
-    }
     __shared__ float red[kWarps - 1][MT * 4][32];
     if (warp > 0) {
 #pragma unroll
@@ -460,29 +452,68 @@ __global__ void __launch_bounds__(kWarps * 32, 7) w8a16_stream_fast_kernel(const
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[mt][j] += red[w][mt * 4 + j][lane];
+
+    // the reference's rounding order: GEMM output, product with the scale, sum with the outlier product,
+    // sum with the bias -- each rounded to the activation type
+    const float s0 = ref_round<A>(load_as_float(p.scales, p.scales_dtype, n0 + g));
+    const float s1 = ref_round<A>(load_as_float(p.scales, p.scales_dtype, n0 + g + 8));
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        acc[mt][0] = ref_round<A>(ref_round<A>(acc[mt][0]) * s0); acc[mt][1] = ref_round<A>(ref_round<A>(acc[mt][1]) * s0);
+        acc[mt][2] = ref_round<A>(ref_round<A>(acc[mt][2]) * s1); acc[mt][3] = ref_round<A>(ref_round<A>(acc[mt][3]) * s1);
+    }
+    if (p.KO > 0) {
+        const A* xo = static_cast<const A*>(p.xo);
+        const A* wo = static_cast<const A*>(p.wo);
+        float side[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) side[mt][j] = 0.0f;
+        const int64_t osteps = (p.KO + 15) / 16;
+        for (int64_t st = 0; st < osteps; ++st) {
+            const int64_t k = st * 16 + t * 4;
+            uint32_t a0[2], a1[2];
+            load_acts<A, 1>(wo + (n0 + g) * p.KO, k, p.KO, true, a0);
+            load_acts<A, 1>(wo + (n0 + g + 8) * p.KO, k, p.KO, true, a1);
+            const uint32_t a[4] = {a0[0], a1[0], a0[1], a1[1]};
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int64_t m = p.m0 + mt * 8 + g;
+                uint32_t b[2];
+                load_acts<A, 1>(xo + m * p.ldxo, k, p.KO, m < p.M, b);
+                Act<A>::mma(side[mt], a, b[0], b[1]);
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[mt][j] = ref_round<A>(acc[mt][j] + ref_round<A>(side[mt][j]));
+    }
     A* y = static_cast<A*>(p.y);
-    const float b0 = p.bias ? load_as_float(p.bias, p.bias_dtype, n0 + g) : 0.0f;
-    const float b1 = p.bias ? load_as_float(p.bias, p.bias_dtype, n0 + g + 8) : 0.0f;
+    const bool has_bias = p.bias != nullptr;
+    const float b0 = has_bias ? ref_round<A>(load_as_float(p.bias, p.bias_dtype, n0 + g)) : 0.0f;
+    const float b1 = has_bias ? ref_round<A>(load_as_float(p.bias, p.bias_dtype, n0 + g + 8)) : 0.0f;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int64_t m = p.m0 + mt * 8 + 2 * t + j;
             if (m >= p.M) continue;
-            y[m * p.ldy + n0 + g] = Act<A>::from_float(acc[mt][j] + b0);
-            y[m * p.ldy + n0 + g + 8] = Act<A>::from_float(acc[mt][2 + j] + b1);
+            y[m * p.ldy + n0 + g] = Act<A>::from_float(has_bias ? acc[mt][j] + b0 : acc[mt][j]);
+            y[m * p.ldy + n0 + g + 8] = Act<A>::from_float(has_bias ? acc[mt][2 + j] + b1 : acc[mt][2 + j]);
         }
     }
 }
 
 template <typename Elem>
 __global__ void gather_cols_kernel(const Elem* __restrict__ src, int64_t M, int64_t ld_src,
-                                   const int64_t* __restrict__ cols, int64_t ncols, Elem* __restrict__ dst,
-                                   int64_t ld_dst) {
-    const int64_t total = M * ncols;
+                                   const int64_t* __restrict__ cols, int64_t ncols, int64_t ncols_padded,
+                                   Elem* __restrict__ dst, int64_t ld_dst) {
+    const int64_t total = M * ncols_padded;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t m = i / ncols, j = i - m * ncols;
-        dst[m * ld_dst + j] = src[m * ld_src + __ldg(cols + j)];
+        const int64_t m = i / ncols_padded, j = i - m * ncols_padded;
+        dst[m * ld_dst + j] = j < ncols ? src[m * ld_src + __ldg(cols + j)] : Elem(0);
     }
 }
 
@@ -492,7 +523,9 @@ template <typename A, int VEC>
 cudaError_t stream_pick_mt(StreamParams p, cudaStream_t s) {
     const unsigned grid = (unsigned)((p.N + 15) / 16);
     int64_t m0 = 0;
+    int extra = -1;  // launches beyond the one the C entry point accounts for
     while (m0 < p.M) {
+        ++extra;
         const int64_t left = p.M - m0;
         p.m0 = m0;
         if (left > 32) {
@@ -509,6 +542,7 @@ cudaError_t stream_pick_mt(StreamParams p, cudaStream_t s) {
             m0 += 8;
         }
     }
+    if (extra > 0) count_launches(extra);
     return cudaPeekAtLastError();
 }
 
@@ -516,7 +550,9 @@ template <typename A>
 cudaError_t stream_fast(StreamParams p, cudaStream_t s) {
     const unsigned grid = (unsigned)(p.N / 16);
     int64_t m0 = 0;
+    int extra = -1;  // launches beyond the one the C entry point accounts for
     while (m0 < p.M) {
+        ++extra;
         const int64_t left = p.M - m0;
         p.m0 = m0;
         if (left > 8) {
@@ -527,6 +563,7 @@ cudaError_t stream_fast(StreamParams p, cudaStream_t s) {
             m0 += 8;
         }
     }
+    if (extra > 0) count_launches(extra);
     return cudaPeekAtLastError();
 }
 
@@ -556,18 +593,18 @@ cudaError_t launch_w8a16_stream(const W8A16Args& a, cudaStream_t s) {
 }
 
 cudaError_t launch_gather_cols(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
-                               void* dst, int64_t ld_dst, int elem_size, cudaStream_t s) {
-    const int64_t total = M * ncols;
+                               int64_t ncols_padded, void* dst, int64_t ld_dst, int elem_size, cudaStream_t s) {
+    const int64_t total = M * ncols_padded;
     int64_t blocks = (total + 255) / 256;
     if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
     if (blocks < 1) blocks = 1;
     if (elem_size == 2)
         gather_cols_kernel<uint16_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), M, ld_src,
-                                                                        cols, ncols, static_cast<uint16_t*>(dst),
+                                                                        cols, ncols, ncols_padded, static_cast<uint16_t*>(dst),
                                                                         ld_dst);
     else
         gather_cols_kernel<uint32_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint32_t*>(src), M, ld_src,
-                                                                        cols, ncols, static_cast<uint32_t*>(dst),
+                                                                        cols, ncols, ncols_padded, static_cast<uint32_t*>(dst),
                                                                         ld_dst);
     return cudaPeekAtLastError();
 }

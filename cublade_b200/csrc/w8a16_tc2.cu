@@ -115,25 +115,6 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-// Development switches, compiled in only with -DCB_TC_DEVTOOLS (never in the shipped build):
-// CB_DBG(bit) disables parts of the kernel for timing experiments and the host reads tuning knobs
-// from the environment.
-#ifdef CB_TC_DEVTOOLS
-#define CB_DBG(bit) ((p.debug & (bit)) != 0)
-#else
-#define CB_DBG(bit) false
-#endif
-
-#ifdef CB_TC_PROFILE
-__device__ unsigned long long g_prof[32];
-#define PROF_T0() const long long _t0 = clock64()
-#define PROF_ADD(slot) do { if (blockIdx.x == 0) g_prof[slot] += (unsigned long long)(clock64() - _t0); } while (0)
-#define PROF_ADD1(slot) do { if (blockIdx.x == 1) g_prof[slot] += (unsigned long long)(clock64() - _t0); } while (0)
-#else
-#define PROF_T0() do {} while (0)
-#define PROF_ADD(slot) do {} while (0)
-#define PROF_ADD1(slot) do {} while (0)
-#endif
 
 struct PairParams {
     int64_t M, N, K;
@@ -223,15 +204,13 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             for (int t = pair; t < total_tiles && ok; t += num_pairs) {
                 const int row_x = (t % p.tiles_x) * p.tile_x + (int)rank * half_x;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    { PROF_T0(); ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag); PROF_ADD(2); }
+                    { ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag); }
                     if (!ok) break;
-                    { PROF_T0();
-                    mbar_expect_tx(full_x + 8 * s, half_bytes);
+                    { mbar_expect_tx(full_x + 8 * s, half_bytes);
 #pragma unroll
                     for (int u = 0; u < kSub; ++u)
                         tma_load_2d(sx + s * p.x_stage_bytes + u * p.x_sub_bytes, &map_x, kb * kStageK + u * kBlockK, row_x,
-                                    full_x + 8 * s);
-                    PROF_ADD(3); }
+                                    full_x + 8 * s); }
                     if (++s == stages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -246,15 +225,12 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 const int row_w = (t / p.tiles_x) * 256 + (int)rank * kUmmaM;
                 const int row_w_next = ((t + num_pairs) / p.tiles_x) * 256 + (int)rank * kUmmaM;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (CB_DBG(8)) {
-                    } else if (kb + kAhead < num_kb) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kStageK, row_w);
+                    if (kb + kAhead < num_kb) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kStageK, row_w);
                     else if (t + num_pairs < total_tiles) tma_prefetch_l2_2d(&map_w, (kb + kAhead - num_kb) * kStageK, row_w_next);
-                    { PROF_T0(); ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag); PROF_ADD(0); }
+                    { ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag); }
                     if (!ok) break;
-                    { PROF_T0();
-                    mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
-                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kStageK, row_w, full_w8 + 8 * s);
-                    PROF_ADD(1); }
+                    { mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
+                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kStageK, row_w, full_w8 + 8 * s); }
                     if (++s == kStagesW8) { s = 0; ph ^= 1u; }
                 }
             }
@@ -270,12 +246,11 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             bool ok = true, pre = false;
             for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
-                { PROF_T0(); ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag); PROF_ADD(9); }  // both epilogues drained it
+                { ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag); }  // both epilogues drained it
                 if (!ok) break;
                 const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     {
-                        PROF_T0();
                         // `pre` holds the result of the probes issued one stage ago (they overlap the
                         // MMA issue of the previous stage); only on a miss does the thread block here.
                         if (!pre) {
@@ -286,10 +261,8 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                                  (r2 || mbar_wait(full_x + 8 * sx_i, phx, abort_flag)) &&
                                  (r3 || mbar_wait(peer_x + 8 * sx_i, phx, abort_flag));
                         }
-                        PROF_ADD(4);
                     }
                     if (!ok) break;
-                    PROF_T0();
                     tc_fence_after();
                     // ring positions of the NEXT stage, probed now, consumed after this stage is issued
                     uint32_t nsa = sa_i + 1, npha = pha, nsx = sx_i + 1, nphx = phx;
@@ -303,12 +276,11 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         const uint64_t bdesc = make_kmajor_sw128_desc(sx + sx_i * p.x_stage_bytes + u * p.x_sub_bytes);
 #pragma unroll
                         for (int k = 0; k < kBlockK / 16; ++k)
-                            if (!CB_DBG(2)) umma_f16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                            umma_f16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
                                           (kb > 0 || u > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit_pair(empty_a + 8 * sa_i);  // frees the slots in both CTAs once these MMAs retire
                     umma_commit_pair(empty_x + 8 * sx_i);
-                    PROF_ADD(8);
                     pre = n0 && n1 && n2 && n3;
                     sa_i = nsa; pha = npha; sx_i = nsx; phx = nphx;
                 }
@@ -324,7 +296,7 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             uint32_t s = 0, ph = 0;
             for (int64_t i = 0; i < total_kb; ++i) {
                 bool ok;
-                { PROF_T0(); ok = mbar_wait(local + 8 * s, ph, abort_flag); PROF_ADD1(13 + lane); }
+                { ok = mbar_wait(local + 8 * s, ph, abort_flag); }
                 if (!ok) break;
                 mbar_arrive_leader(remote + 8 * s);
                 if (++s == depth) { s = 0; ph ^= 1u; }
@@ -343,8 +315,9 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
             const int64_t n = (int64_t)tn * 256 + (int64_t)rank * kUmmaM + quarter * 32 + lane;
             const bool n_ok = n < p.N;
-            const float scale = n_ok ? load_scalar(p.scales, p.scales_dtype, n) : 0.0f;
-            const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+            const float scale = n_ok ? ref_round<A>(load_scalar(p.scales, p.scales_dtype, n)) : 0.0f;
+            const bool has_bias = p.bias != nullptr;
+            const float bias = (n_ok && has_bias) ? ref_round<A>(load_scalar(p.bias, p.bias_dtype, n)) : 0.0f;
             ok = warp_wait(tmem_full + 8 * acc, acc_ph, abort_flag, lane);
             if (!ok) break;
             tc_fence_after();
@@ -357,14 +330,16 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 for (int c = 0; c < 32; ++c) {
                     const int64_t m = m_base + c0 + c;
                     if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
-                    float v = __uint_as_float(r[c]) * scale;
+                    float v = ref_round<A>(ref_round<A>(__uint_as_float(r[c])) * scale);
                     if (p.KO > 0 && n_ok) {
                         const A* xrow = xo + m * p.ldxo;  // same address in every lane: broadcast load
                         const A* wrow = wo + n * p.KO;
+                        float side = 0.0f;
                         for (int j = 0; j < (int)p.KO; ++j)
-                            v = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), v);
+                            side = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), side);
+                        v = ref_round<A>(v + ref_round<A>(side));
                     }
-                    v += bias;
+                    if (has_bias) v = ref_round<A>(v + bias);
                     if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
                 }
             }
@@ -390,7 +365,6 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         {
             for (int64_t st = group; st < total_st && ok; st += kConvWarps / kConvGroupWarps) {
                 {
-                    PROF_T0();
                     int okw = 1;
                     if (lane == 0) {
                         const bool r0 = mbar_try(full_w8 + 8 * s_w, ph_w), r1 = mbar_try(empty_a + 8 * s_a, ph_a ^ 1u);
@@ -398,12 +372,10 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                                (r1 || mbar_wait(empty_a + 8 * s_a, ph_a ^ 1u, abort_flag))) ? 1 : 0;
                     }
                     ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
-                    if (cid == 0 && group == 0) PROF_ADD(10);
                 }
                 if (!ok) break;
-                PROF_T0();
                 tc_fence_after();
-                if (!CB_DBG(1)) {
+                {
 #pragma unroll
                 for (int pass = 0; pass < (kUmmaM * kStageK / 16) / (kConvGroupWarps * 32); ++pass) {
                     // 16-byte chunk `id` of the int8 stage: 128-byte rows, chunk jc covers k = 16 jc .. +15
@@ -434,13 +406,12 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                                  : "memory");
                 }
                 }
-                if (!CB_DBG(4)) fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
+                fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(full_a + 8 * s_a);
                     mbar_arrive(empty_w8 + 8 * s_w);
                 }
-                if (cid == 0 && group == 0) PROF_ADD(12);
                 for (int q = 0; q < kConvWarps / kConvGroupWarps; ++q) advance();
             }
         }
@@ -509,17 +480,6 @@ int pick_pair_tile_x(int64_t M, int64_t N, int pairs) {
 
 unsigned int* w8a16_tc_error_word();  // w8a16_tc.cu
 
-#ifdef CB_TC_PROFILE
-extern "C" int cb_tc_profile_read(unsigned long long* out32, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out32, g_prof, sizeof(unsigned long long) * 32);
-    if (reset) {
-        unsigned long long z[32] = {};
-        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
 
 bool w8a16_tc_pair_supported(const W8A16Args& a) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -542,14 +502,6 @@ cudaError_t launch_w8a16_tc_pair(const W8A16Args& a, cudaStream_t s) {
     p.y = a.y; p.ldy = a.ldy;
     p.tile_x = pick_pair_tile_x(a.M, a.N, pairs_avail);
     p.debug = 0;
-#ifdef CB_TC_DEVTOOLS
-    {
-        const char* d = getenv("CB_TC_DEBUG");
-        p.debug = d ? atoi(d) : 0;
-        const char* tx = getenv("CB_TC_TILE_X");
-        if (tx) p.tile_x = atoi(tx);
-    }
-#endif
     p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
     p.tiles_n = (int)((a.N + 255) / 256);
     p.error_flag = w8a16_tc_error_word();
@@ -609,10 +561,6 @@ cudaError_t launch_w8a16_tc_pair(const W8A16Args& a, cudaStream_t s) {
             max_clusters[dev][which] = n;
         }
         int cap = (dev >= 0 && dev < 64) ? max_clusters[dev][which] : pairs_avail;
-#ifdef CB_TC_DEVTOOLS
-        const char* e = getenv("CB_TC_PAIRS");
-        if (e) cap = atoi(e);
-#endif
         if (pairs > cap) cfg.gridDim = dim3((unsigned)(2 * cap));
     }
     void* args[3] = {(void*)&map_x, (void*)&map_w, (void*)&p};

@@ -113,23 +113,6 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t tadd
     }
 }
 
-#ifdef CB_TC_PROFILE
-// development only: cycle counters of CTA 0 -- [0] x producer waiting for a free stage, [1] w producer waiting,
-// [2] MMA thread waiting for a full stage, [3] MMA thread issuing + committing, [4] MMA thread waiting for the
-// accumulator, [5] k-blocks, [6] total cycles of the MMA thread, [7] epilogue warp 2 waiting for tmem_full,
-// [8] epilogue warp 2 draining
-__device__ unsigned long long g_w8a8_prof[16];
-// counters live in registers of the measuring thread and are written once when its role ends
-#define W8_PROF_DECL unsigned long long prof_acc[4] = {0, 0, 0, 0};
-#define W8_PROF_T0 const long long prof_t0 = clock64();
-#define W8_PROF_ADD(i) prof_acc[i] += (unsigned long long)(clock64() - prof_t0);
-#define W8_PROF_FLUSH(i, slot) if (blockIdx.x == 0) g_w8a8_prof[slot] = prof_acc[i];
-#else
-#define W8_PROF_DECL
-#define W8_PROF_T0
-#define W8_PROF_ADD(i)
-#define W8_PROF_FLUSH(i, slot)
-#endif
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -169,14 +152,11 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const bool is_x = warp == 0;
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            W8_PROF_DECL
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int row = is_x ? (t % p.tiles_x) * p.tile_x : (t / p.tiles_x) * kTileN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     {
-                        W8_PROF_T0
                         ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);
-                        W8_PROF_ADD(0)
                     }
                     if (!ok) break;
                     if (is_x) {
@@ -189,36 +169,26 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
-            W8_PROF_FLUSH(0, is_x ? 0 : 1)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            W8_PROF_DECL
             const uint32_t idesc = make_idesc_i8((uint32_t)p.tile_x);
             uint32_t s = 0, ph = 0, it = 0;
             bool ok = true;
-#ifdef CB_TC_PROFILE
-            const long long prof_start = clock64();
-#endif
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
                 {
-                    W8_PROF_T0
                     ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
-                    W8_PROF_ADD(2)
                 }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     {
-                        W8_PROF_T0
                         ok = mbar_wait(full + 8 * s, ph, abort_flag);
-                        W8_PROF_ADD(0)
                     }
                     if (!ok) break;
-                    W8_PROF_T0
                     tc_fence_after();
                     const uint64_t adesc = make_kmajor_sw128_desc(sw + s * kBytesW);
                     const uint64_t bdesc = make_kmajor_sw128_desc(sx + s * kBytesX);
@@ -228,26 +198,17 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         umma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty + 8 * s);  // the stage is free once these MMAs retire
-                    W8_PROF_ADD(1)
-#ifdef CB_TC_PROFILE
-                    prof_acc[3] += 1;
-#endif
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit(tmem_full + 8 * acc);
             }
-#ifdef CB_TC_PROFILE
-            if (blockIdx.x == 0) g_w8a8_prof[6] = (unsigned long long)(clock64() - prof_start);
-#endif
-            W8_PROF_FLUSH(0, 2) W8_PROF_FLUSH(1, 3) W8_PROF_FLUSH(2, 4) W8_PROF_FLUSH(3, 5)
         }
     } else if (warp < 2 + kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
         const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes 32 * (warp % 4) .. + 31
         uint32_t it = 0;
         bool ok = true;
-        W8_PROF_DECL
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
             const int tx = t % p.tiles_x, tn = t / p.tiles_x;
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
@@ -256,23 +217,18 @@ w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const float wscale = n_ok ? load_scalar(p.ws, p.ws_dtype, n) : 0.0f;
             const float bias = (n_ok && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
             {
-                W8_PROF_T0
                 int okw = 1;
                 if (lane == 0) okw = mbar_wait(tmem_full + 8 * acc, acc_ph, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
-                W8_PROF_ADD(0)
             }
             if (!ok) break;
             tc_fence_after();
-            W8_PROF_T0
             drain_accumulator<T>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX, (warp - 2) >> 2, kEpiWarps / 4,
                                  (int64_t)tx * p.tile_x, n, n_ok, wscale, bias, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
-            W8_PROF_ADD(1)
         }
-        if (warp == 2 && lane == 0) { W8_PROF_FLUSH(0, 7) W8_PROF_FLUSH(1, 8) }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -628,9 +584,6 @@ cudaError_t launch_t(const W8A8Args& a, cudaStream_t s) {
     p.error_flag = w8a16_tc_error_word();
     if (!p.error_flag) return cudaErrorUnknown;
     bool use_pair = a.M >= 256 && a.N >= 256;
-#ifdef CB_TC_DEVTOOLS
-    if (const char* f = getenv("CB_W8A8_PAIR")) use_pair = atoi(f) != 0;
-#endif
     if (use_pair) return launch_pair_t<T>(a, p, s);
     p.tile_x = pick_tile_x(a.M, a.N, sms);
     p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
@@ -662,14 +615,3 @@ cudaError_t launch_w8a8(const W8A8Args& a, cudaStream_t s) {
 
 }  // namespace cb
 
-#ifdef CB_TC_PROFILE
-extern "C" int cb_dev_w8a8_profile(unsigned long long* host, int reset) {
-    cudaDeviceSynchronize();
-    int e = (int)cudaMemcpyFromSymbol(host, cb::g_w8a8_prof, sizeof(unsigned long long) * 16);
-    if (reset) {
-        unsigned long long z[16] = {0};
-        e |= (int)cudaMemcpyToSymbol(cb::g_w8a8_prof, z, sizeof(z));
-    }
-    return e;
-}
-#endif

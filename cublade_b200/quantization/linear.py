@@ -3,8 +3,9 @@
 Buffer names, dtypes and shapes (``int8_weights [out, in]``, ``scales [out]``, ``outlier_weights``,
 ``normal_cols``, ``outlier_cols``) and the constructor / ``quantize`` / ``forward`` contract follow
 cublade/quantization/linear.py:8-137, so ``state_dict()`` is interchangeable.  The forward pass
-is one fused kernel (see ``bindings/w8a16.py``); it rounds once at the end, where the reference
-rounds after the GEMM, after the scale and after the bias.
+is one fused kernel (see ``bindings/w8a16.py``) whose epilogue rounds in the same places as the
+reference's chain of kernels, so outputs agree with the reference's bit for bit up to the order of
+the fp32 accumulation.
 """
 from __future__ import annotations
 
@@ -75,8 +76,28 @@ class cuBladeW8A16LinearLayer(nn.Module):
         self._dev_cache[key] = (src, src._version, moved)
         return moved
 
+    def _padded_weights(self, dev: torch.device, width: int) -> torch.Tensor:
+        """``int8_weights`` on ``dev`` with zero columns appended up to ``width`` (cached like ``_on``).
+
+        The tensor-core kernels fetch the int8 rows with TMA, whose row stride must be a multiple of 16
+        bytes; ``in_features - n_outliers`` seldom is.  ``state_dict()`` keeps the reference's
+        ``[out, in - n_outliers]`` shape -- the padded copy lives only in this cache."""
+        src = self.int8_weights
+        key = ("int8_weights_padded", dev, width)
+        hit = self._dev_cache.get(key)
+        if hit is not None and hit[0] is src and hit[1] == src._version:
+            return hit[2]
+        padded = torch.zeros((src.shape[0], width), dtype=torch.int8, device=dev)
+        padded[:, : src.shape[1]].copy_(src)
+        self._dev_cache[key] = (src, src._version, padded)
+        return padded
+
     def forward(self, x: torch.Tensor):
-        """``y = x @ dequant(W).T (+ outlier columns in 16-bit) (+ bias)`` on the GPU, shape ``[..., out]``."""
+        """``y = x @ dequant(W).T (+ outlier columns in 16-bit) (+ bias)`` on the GPU, shape ``[..., out]``.
+
+        The result is rounded to the activation dtype where the reference's forward materialises a
+        tensor -- after the GEMM, after the scales, after adding the outlier product, after the bias
+        (cublade/quantization/linear.py:97-135) -- inside the one fused kernel."""
         if not x.is_cuda:
             raise ValueError(
                 f"cuBladeW8A16LinearLayer.forward: input must be on CUDA, got device={x.device} "
@@ -100,9 +121,21 @@ class cuBladeW8A16LinearLayer(nn.Module):
             normal_idx = self._on("normal_cols", dev)
             outlier_idx = self._on("outlier_cols", dev)
             w_out = self._on("outlier_weights", dev, x2d.dtype)
-            x_normal = gather_columns(x2d, normal_idx)
+            kn = wq.shape[1]
+            if kn % 16 and x2d.shape[0] > 16:  # the tensor-core kernels need 16-byte int8 rows: pad K with zeros
+                width = (kn + 15) // 16 * 16
+                wq = self._padded_weights(dev, width)
+                x_normal = gather_columns(x2d, normal_idx, pad_to=width)
+            else:
+                x_normal = gather_columns(x2d, normal_idx)
             x_out = gather_columns(x2d, outlier_idx)
             y2d = w8a16_linear(x_normal, wq, scales, bias, x_out, w_out)
+        elif self.in_features % 16 and x2d.shape[0] > 16:
+            width = (self.in_features + 15) // 16 * 16
+            every = self._dev_cache.get(("arange", dev))
+            if every is None:
+                every = self._dev_cache[("arange", dev)] = torch.arange(self.in_features, device=dev)
+            y2d = w8a16_linear(gather_columns(x2d, every, pad_to=width), self._padded_weights(dev, width), scales, bias)
         else:
             y2d = w8a16_linear(x2d, wq, scales, bias)
         return y2d.view(*lead, self.out_features)

@@ -146,6 +146,15 @@ int32_t cb_device_error_state(uint32_t* host_flag, void* stream);
 int32_t cb_gather_columns(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols, void* dst,
                           int64_t ld_dst, int32_t elem_size, void* stream);
 
+/* The same gather with columns ncols .. ncols_padded - 1 of every dst row written as zero
+ * (ncols <= ncols_padded <= ld_dst).  The tensor-core kernels behind cb_w8a16_linear load the int8
+ * rows with TMA, which needs a row stride of K % 16 == 0 bytes; the LLM.int8 split leaves
+ * K = in_features - n_outliers (cublade/quantization/linear.py:48-66), rarely such a multiple.  A caller
+ * keeps a copy of the int8 weights with zero columns up to the next multiple of 16, re-packs the
+ * activations with this call to the same width and passes the padded K: the zero columns add nothing. */
+int32_t cb_gather_columns_padded(const void* src, int64_t M, int64_t ld_src, const int64_t* cols, int64_t ncols,
+                                 int64_t ncols_padded, void* dst, int64_t ld_dst, int32_t elem_size, void* stream);
+
 /* ------------------------------------------------------------------------
  * Dense GEMM  C[M, N] = A[M, K] . B[K, N], all row-major, on tcgen05 / TMEM.
  * replaces wmma_gemm(A, B, acc_dtype)

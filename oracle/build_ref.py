@@ -16,6 +16,16 @@ used exclusively by ``tests/`` as a second, device-side checker and by
 ``tests/golden/make_ref_gpu_golden.py`` to record the reference's real outputs.
 The shipped package never imports them.
 
+For the W8A16 layer the reference's arithmetic is Python + Triton
+(``cublade/quantization/linear.py``, ``cublade/bindings/triton/matmul.py``), so there is nothing
+to compile ahead of time: ``install_package`` pip-installs the unmodified reference into
+``oracle/_ref/site`` (a build product, like the ``.so`` files beside it) so that a GPU box
+without the checkout can ``import cublade`` and run the reference's own
+``cuBladeW8A16LinearLayer`` -- which ``tests/golden/make_ref_w8a16_golden.py`` does to record the
+layer's real outputs.  ``prebuild_jit`` warms the reference loader's JIT cache for the one CUDA
+module that layer's ``quantize()`` needs, with the loader's own name, flags and source path, so
+the box does not spend minutes compiling it.
+
 Usage:  python oracle/build_ref.py [--reference /path/to/cublade]
 """
 from __future__ import annotations
@@ -65,6 +75,59 @@ def build_all(reference: Path, verbose: bool = False) -> None:
             is_python_module=True,
         )
         print(f"[oracle/_ref] built {name}", flush=True)
+    install_package(reference)
+    prebuild_jit(verbose)
+
+
+SITE = OUT / "site"          # pip --target directory holding the installed reference package
+JIT_CACHE = OUT / "torch_ext"  # TORCH_EXTENSIONS_DIR for the reference's own JIT loader
+
+
+def install_package(reference: Path) -> Path:
+    """``pip install --no-deps --target oracle/_ref/site`` of the unmodified reference.
+
+    The checkout is read-only and setuptools writes ``build/`` and ``*.egg-info`` beside
+    ``pyproject.toml``, so the wheel is built from a temporary copy."""
+    import shutil
+    import subprocess
+    import tempfile
+
+    if (SITE / "cublade" / "quantization" / "linear.py").exists():
+        return SITE
+    with tempfile.TemporaryDirectory() as tmp:
+        copy = Path(tmp) / "cublade_src"
+        shutil.copytree(reference, copy, ignore=shutil.ignore_patterns(".git"))
+        cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps",
+               "--find-links", "/opt/wheelhouse", "--target", str(SITE), str(copy)]
+        subprocess.run(cmd, check=True, capture_output=True)
+    print(f"[oracle/_ref] installed the reference package into {SITE}", flush=True)
+    return SITE
+
+
+def reference_env() -> dict:
+    """Environment under which the installed reference is imported (here and on a GPU box): its
+    import-time warm-up off, its JIT cache inside ``oracle/_ref``, and a fixed arch list so that
+    the compile command -- and with it ninja's up-to-date check -- is the same on both machines."""
+    return {"CUBLADE_SKIP_WARMUP": "1", "TORCH_EXTENSIONS_DIR": str(JIT_CACHE), "TORCH_CUDA_ARCH_LIST": "10.0",
+            "MAX_JOBS": "8"}
+
+
+def prebuild_jit(verbose: bool = False) -> None:
+    """Compile ``cublade_quantize_int8`` into the JIT cache exactly as ``cublade/_loader.py:92-111``
+    would on a B200 (``-arch=sm_100``, no fast-math for the INT8 module)."""
+    if not SITE.exists():
+        return
+    os.environ.update(reference_env())
+    from torch.utils.cpp_extension import load
+
+    csrc = SITE / "cublade" / "kernels" / "cuda"
+    name = "cublade_quantize_int8"
+    if (JIT_CACHE / name / f"{name}.so").exists():
+        return
+    load(name=name, sources=[str(csrc / "quantization" / "quantize_int8.cu")],
+         extra_cuda_cflags=["-O3", "-std=c++17", "-arch=sm_100", "--expt-relaxed-constexpr"],
+         extra_include_paths=[str(csrc)], extra_ldflags=None, verbose=verbose)
+    print(f"[oracle/_ref] JIT cache warmed for {name}", flush=True)
 
 
 def load_ref(name: str):

@@ -55,3 +55,51 @@ def int8_group_cases():
         "i8g_g4096": ((torch.randn(3, 4096, generator=_g(43)) * 2.0).to(torch.float16), 4096),
         "i8g_fp32_g16": (torch.randn(64, 16, generator=_g(44)), 16),
     }
+
+
+# ------------------------------------------------------------------------------------------------
+# W8A16 linear layer at the benchmark shape (N = 14336, K = 4096), plain and LLM.int8 variants
+# ------------------------------------------------------------------------------------------------
+W8A16_N, W8A16_K = 14336, 4096
+W8A16_MS = (1, 16, 128, 2048)
+W8A16_OUTLIER_COLS = 8
+
+
+def w8a16_weight(outliers: bool):
+    """(weight, outlier columns, bias).  Plain: the bf16 N(0, 0.02) weight of the benchmark, no bias.
+    LLM.int8 variant: float32 master weights in which every seventh row of 8 seeded columns is 7.5, so
+    that the reference's weight-side detector (cublade/quantization/outlier_utils.py:33-35, threshold
+    6.0) selects exactly those columns; K - 8 = 4088 keeps float32 rows 16-byte multiples
+    (quantize_int8.cu:496-498).  That variant carries a bias, the plain one does not."""
+    from cublade_b200 import workloads as W
+
+    w, _, _ = W.w8a16_case(1, N=W8A16_N, K=W8A16_K)
+    if not outliers:
+        return w, [], None
+    g = _g(33)
+    cols = sorted(torch.randperm(W8A16_K, generator=g)[:W8A16_OUTLIER_COLS].tolist())
+    w32 = w.float()
+    w32[:, cols] = torch.where(torch.arange(W8A16_N)[:, None] % 7 == 0, 7.5, w32[:, cols])
+    bias = torch.randn(W8A16_N, generator=g).to(torch.bfloat16)
+    return w32, cols, bias
+
+
+def w8a16_activations(M: int, cols=()):
+    """bf16 activations [M, K] of the benchmark (``workloads.w8a16_case(M)``: seeded N(0, 1)); the
+    columns ``cols`` are scaled by 20 (exact in bf16 up to the rounding of the product)."""
+    from cublade_b200 import workloads as W
+
+    _, x, _ = W.w8a16_case(M, N=W8A16_N, K=W8A16_K)
+    if len(cols):
+        x = x.float()
+        x[:, list(cols)] *= 20.0
+        x = x.to(torch.bfloat16)
+    return x
+
+
+def w8a16_golden_rows(M: int, outliers: bool):
+    """Rows of the [M, N] output kept in the golden file (all of them for M <= 16)."""
+    if M <= 16:
+        return list(range(M))
+    keep = (8 if outliers else 16) if M <= 128 else (8 if outliers else 32)
+    return sorted(torch.randperm(M, generator=_g(400 + M))[:keep].tolist())

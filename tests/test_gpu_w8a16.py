@@ -239,3 +239,110 @@ def test_more_tiles_than_sms(M, N, K):
     y = w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda(), path=3)
     _check(y, O.w8a16_forward(x, lay, b), f"M={M} N={N} K={K}")
     assert Nat.device_error_state() == 0
+
+
+# ------------------------------------------------------------------------------------------------
+# Against what the reference's own layer computed on a B200 (tests/golden/ref_w8a16_golden.npz,
+# recorded by tests/golden/make_ref_w8a16_golden.py from an unmodified install of the reference)
+# ------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def ref_gold():
+    from pathlib import Path
+
+    import numpy as np
+
+    return dict(np.load(Path(__file__).parent / "golden" / "ref_w8a16_golden.npz"))
+
+
+@pytest.fixture(scope="module", params=[False, True], ids=["plain", "outlier8"])
+def ref_variant(request):
+    import cublade_b200 as cb
+    from tests.golden import cases
+
+    outliers = request.param
+    w, cols, bias = cases.w8a16_weight(outliers)
+    layer = cb.cuBladeW8A16LinearLayer(cases.W8A16_K, cases.W8A16_N, bias=bias is not None, dtype=torch.bfloat16,
+                                       handle_outliers=outliers, outlier_threshold=6.0)
+    layer.quantize(w)
+    if bias is not None:
+        layer.bias = torch.nn.Parameter(bias.clone())
+    return ("w8a16_outlier8" if outliers else "w8a16_plain"), outliers, cols, layer.cuda()
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 2048])
+def test_forward_against_the_reference_layers_recorded_outputs(ref_gold, ref_variant, M):
+    """Benchmark shape (N = 14336, K = 4096; K - 8 = 4088 int8 columns in the LLM.int8 variant, which the layer
+    pads to 4096 for the tensor-core kernels).  Gate: the stated tolerance; and because the epilogue rounds in
+    the reference's places, fewer than 0.5 % of the bf16 values may differ at all (accumulation order)."""
+    import hashlib
+
+    from tests.golden import cases
+
+    tag, outliers, cols, layer = ref_variant
+    digest = hashlib.sha256(layer.int8_weights.cpu().contiguous().view(torch.uint8).numpy().tobytes()).digest()
+    assert digest == ref_gold[f"{tag}.int8_sha256"].tobytes(), "int8 weights differ from the reference layer's"
+    assert torch.equal(layer.scales.cpu().view(torch.int16), torch.from_numpy(ref_gold[f"{tag}.scales"]))
+    if outliers:
+        assert layer.outlier_cols.tolist() == cols and layer.int8_weights.shape == (cases.W8A16_N, cases.W8A16_K - 8)
+    rows = ref_gold[f"{tag}.M{M}.rows"].tolist()
+    y_ref = torch.from_numpy(ref_gold[f"{tag}.M{M}.y"]).view(torch.bfloat16)
+    y = layer(cases.w8a16_activations(M, cols).cuda())[rows].cpu()
+    _check(y, y_ref, f"{tag} M={M} vs the reference's recorded output")
+    ne = int((y.view(torch.int16) != y_ref.view(torch.int16)).sum())
+    assert ne <= 5e-3 * y.numel(), f"{ne} of {y.numel()} bf16 values differ from the reference"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K,n_out", [(200, 512, 1032, 8), (300, 640, 4096, 8), (200, 256, 520, 0)])
+def test_int8_rows_that_are_not_16_byte_multiples_take_the_tensor_core_path(M, N, K, n_out, dtype):
+    """in_features - n_outliers (or in_features itself) = 8 mod 16: the layer pads K with zero columns in a cached
+    copy of the int8 weights and in the re-packed activations, so the tensor-core kernel serves the call (one
+    launch after the gathers, not a chain of streaming launches); the state dict keeps the unpadded shape."""
+    import cublade_b200 as cb
+    from cublade_b200 import _native as Nat
+
+    g = torch.Generator().manual_seed(M + N + K)
+    w = torch.randn(N, K, generator=g) * 0.05
+    cols = sorted(torch.randperm(K, generator=g)[:n_out].tolist())
+    if n_out:
+        w[:, cols] = torch.where(torch.arange(N)[:, None] % 5 == 0, 7.0, w[:, cols])
+    x = torch.randn(M, K, generator=g)
+    if n_out:
+        x[:, cols] *= 20.0
+    x = x.to(dtype)
+    bias = torch.randn(N, generator=g).to(dtype)
+    layer = cb.cuBladeW8A16LinearLayer(K, N, bias=True, dtype=dtype, handle_outliers=n_out > 0)
+    layer.quantize(w if n_out else w.to(dtype))
+    layer.bias = torch.nn.Parameter(bias.clone())
+    layer = layer.cuda()
+    kn = K - n_out
+    assert kn % 16 == 8 and layer.int8_weights.shape == (N, kn)
+    layer(x.cuda())  # fills the padded-weight cache
+    before = Nat.launch_count()
+    y = layer(x.cuda())
+    gathers = 2 if n_out else 1
+    assert Nat.launch_count() - before <= gathers + 2, "gathers + one GEMM launch (+ its K-split fix-up), no streaming chain"
+    lay = O.w8a16_quantize(w if n_out else w.to(dtype), dtype, outlier_cols=cols or None)
+    _check(y, O.w8a16_forward(x, lay, bias), "padded K vs reference rounding order")
+    _check(y, O.w8a16_forward_fp64(x, lay, bias), "padded K vs exact")
+    assert set(layer.state_dict()["int8_weights"].shape) == {N, kn}
+    assert Nat.device_error_state() == 0
+
+
+@pytest.mark.parametrize("M", [8, 150])
+def test_more_than_64_outlier_columns(M):
+    """KO = 65 outlier columns: served by the same kernels (the side product loops over any count)."""
+    from cublade_b200.bindings.w8a16 import w8a16_linear
+
+    N, K, KO = 384, 1024, 65
+    g = torch.Generator().manual_seed(M)
+    dtype = torch.bfloat16
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    xo = (torch.randn(M, KO, generator=g) * 20).to(dtype)
+    wo = (torch.randn(N, KO, generator=g) * 0.05).to(dtype)
+    lay = O.w8a16_quantize(w, dtype)
+    ref = O.w8a16_forward_fp64(x, lay) + xo.double() @ wo.double().T
+    for path in (0, 3) if M > 16 else (0, 1):
+        y = w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), None, xo.cuda(), wo.cuda(), path=path)
+        _check(y, ref, f"KO=65 path {path}")

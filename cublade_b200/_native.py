@@ -64,6 +64,10 @@ SIGNATURES = {
     "cb_quantize_per_axis_int8": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p,
                                             c_void_p, c_void_p]),
     "cb_dequantize_per_axis_int8": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p]),
+    "cb_quantize_per_group_axis_int8": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p,
+                                                  c_void_p, c_void_p]),
+    "cb_dequantize_per_group_axis_int8": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int32,
+                                                    c_void_p, c_void_p]),
     "cb_rmsnorm_quantize": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_void_p, c_float, c_float, c_int32, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_gather_columns": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p]),

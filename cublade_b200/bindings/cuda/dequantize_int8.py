@@ -70,3 +70,29 @@ def dequantize_per_axis_int8(q: torch.Tensor, scale: torch.Tensor, axis: int,
         N.check(N.lib().cb_dequantize_per_axis_int8(q.data_ptr(), scale.data_ptr(), outer, C, inner, N.dtype_code(dtype),
                                                     y.data_ptr(), N.stream_ptr(q)))
     return y
+
+
+def dequantize_per_group_axis_int8(q: torch.Tensor, scale: torch.Tensor, axis: int, group_size: int,
+                                   dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Inverse of ``quantize_per_group_axis_int8``: ``y = dtype(float(q) * scale[group])`` with the groups along
+    ``axis`` and the scales flat in the reference's moved-axis order (cublade/quantization/dequantizers.py:58-72),
+    computed where the codes lie."""
+    check_dequant_input(q, scale, dtype, torch.int8, "torch.int8")
+    require(q.dim() >= 1, "q must have at least 1 dim")
+    require(-q.dim() <= axis < q.dim(), f"axis {axis} out of range for a {q.dim()}-d tensor")
+    axis %= q.dim()
+    outer = 1
+    for d in q.shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in q.shape[axis + 1:]:
+        inner *= d
+    C = q.size(axis)
+    require(scale.is_contiguous() and scale.numel() * int(group_size) == q.numel(),
+            "scale must be contiguous with one entry per group")
+    with N.device_guard(q):
+        y = torch.empty(q.shape, dtype=dtype, device=q.device)
+        N.check(N.lib().cb_dequantize_per_group_axis_int8(q.data_ptr(), scale.data_ptr(), outer, C, inner,
+                                                          int(group_size), N.dtype_code(dtype), y.data_ptr(),
+                                                          N.stream_ptr(q)))
+    return y

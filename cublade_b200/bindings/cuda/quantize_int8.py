@@ -84,3 +84,34 @@ def quantize_per_axis_int8(x: torch.Tensor, axis: int, eps: float = 1e-12) -> tu
         N.check(N.lib().cb_quantize_per_axis_int8(x.data_ptr(), N.dtype_code(x.dtype), outer, C, inner, float(eps),
                                                   q.data_ptr(), scale.data_ptr(), scratch.data_ptr(), N.stream_ptr(x)))
     return q, scale
+
+
+def _outer_c_inner(shape, axis):
+    outer = 1
+    for d in shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in shape[axis + 1:]:
+        inner *= d
+    return outer, shape[axis], inner
+
+
+def quantize_per_group_axis_int8(x: torch.Tensor, axis: int, group_size: int,
+                                 eps: float = 1e-12) -> tuple[torch.Tensor, torch.Tensor]:
+    """Groups of ``group_size`` consecutive indices along ``axis`` (any axis) of a contiguous tensor,
+    quantized where they lie.  Equals the reference's route for ``mode="group"`` with a non-last
+    ``ch_axis`` (cublade/quantization/quantizers.py:122-132: move the axis last with a copy, quantize
+    rows of ``group_size``, move the codes back with a second copy) bit for bit, scales in the same flat
+    order, without either copy.  Returns ``(q int8 like x, scale float32 [x.numel() // group_size])``."""
+    check_quant_input(x, _ALLOWED, _TEXT)
+    require(x.dim() >= 1, "x must have at least 1 dim for per-group quant")
+    require(-x.dim() <= axis < x.dim(), f"axis {axis} out of range for a {x.dim()}-d tensor")
+    axis %= x.dim()
+    outer, C, inner = _outer_c_inner(tuple(x.shape), axis)
+    with N.device_guard(x):
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        scale = torch.empty((x.numel() // max(int(group_size), 1),), dtype=torch.float32, device=x.device)
+        N.check(N.lib().cb_quantize_per_group_axis_int8(x.data_ptr(), N.dtype_code(x.dtype), outer, C, inner,
+                                                        int(group_size), float(eps), q.data_ptr(), scale.data_ptr(),
+                                                        N.stream_ptr(x)))
+    return q, scale

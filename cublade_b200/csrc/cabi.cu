@@ -342,6 +342,32 @@ int32_t cb_dequantize_per_axis_int8(const void* q, const float* scale, int64_t o
                        "cb_dequantize_per_axis_int8", 1);
 }
 
+int32_t cb_quantize_per_group_axis_int8(const void* x, int32_t dtype, int64_t outer, int64_t C, int64_t inner,
+                                        int64_t group_size, float eps, void* q, float* scale, void* stream) {
+    const char* name = "cb_quantize_per_group_axis_int8";
+    if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "%s: x must be float16, bfloat16 or float32", name);
+    if (group_size <= 0 || group_size > 4096) return fail(CB_ERR_RANGE, "group_size must be in (0, 4096]");
+    if (outer < 0 || C < 0 || inner < 0) return fail(CB_ERR_ARGUMENT, "%s: negative size", name);
+    if (C % group_size != 0) return fail(CB_ERR_ARGUMENT, "%s: group_size must divide C", name);
+    if (outer * C * inner == 0) return CB_OK;
+    if (!x || !q || !scale) return fail(CB_ERR_ARGUMENT, "%s: null pointer", name);
+    return cuda_result(cb::launch_quant_group_axis(x, dtype, outer, C, inner, (int)group_size, eps, q, scale,
+                                                   as_stream(stream)), name, 1);
+}
+
+int32_t cb_dequantize_per_group_axis_int8(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner,
+                                          int64_t group_size, int32_t out_dtype, void* y, void* stream) {
+    const char* name = "cb_dequantize_per_group_axis_int8";
+    if (out_dtype != CB_F16 && out_dtype != CB_BF16) return fail(CB_ERR_DTYPE, "%s: out_dtype must be float16 or bfloat16", name);
+    if (group_size <= 0 || group_size > 4096) return fail(CB_ERR_RANGE, "group_size must be in (0, 4096]");
+    if (outer < 0 || C < 0 || inner < 0) return fail(CB_ERR_ARGUMENT, "%s: negative size", name);
+    if (C % group_size != 0) return fail(CB_ERR_ARGUMENT, "%s: group_size must divide C", name);
+    if (outer * C * inner == 0) return CB_OK;
+    if (!q || !scale || !y) return fail(CB_ERR_ARGUMENT, "%s: null pointer", name);
+    return cuda_result(cb::launch_dequant_group_axis(q, scale, outer, C, inner, (int)group_size, out_dtype, y,
+                                                     as_stream(stream)), name, 1);
+}
+
 int32_t cb_rmsnorm_quantize(const void* x, int32_t dtype, int64_t rows, int64_t hidden, const void* gamma, float rms_eps,
                             float q_eps, int32_t code_kind, void* q, float* scale, void* y_out, float* rstd_out,
                             void* stream) {

@@ -17,6 +17,34 @@ inline int dtype_size(int dt) { return dt == kF32 ? 4 : 2; }
 // number of SMs of the current device (cached per device)
 int sm_count();
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched through launch_dependent() may become resident while the kernel before it in the
+// stream is still running; it must call pdl_wait() before it touches anything that kernel (or any
+// earlier one) wrote -- until then it may only read memory no kernel in flight writes (its inputs).
+// The kernel before it calls pdl_trigger() to allow that early start.  Both are no-ops when the launch
+// carries no such edge, so the same kernels also run from plain launches.  Stream capture records the
+// edge, so graph replays keep the overlap.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ---- per-tensor (two phase) ------------------------------------------------
 // amax[0] = max(amax[0], max|x|); amax must hold a non-negative float (0 to start).
 cudaError_t launch_amax_tensor(const void* x, int dtype, int64_t n, float* amax, cudaStream_t s);
@@ -39,6 +67,14 @@ cudaError_t launch_quant_axis(const void* x, int dtype, int64_t outer, int64_t C
                               float* scale_out, float* scratch, cudaStream_t s);
 cudaError_t launch_dequant_axis(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner, int out_dtype,
                                 void* y, cudaStream_t s);
+
+// ---- per-group INT8 with the groups along a non-last axis of a contiguous [outer, C, inner] tensor, in place ----
+// G consecutive indices of C form a group for every (outer, inner) position; C % G == 0.
+// scale_out: outer * inner * (C / G) floats, index (o * inner + i) * (C / G) + c / G.
+cudaError_t launch_quant_group_axis(const void* x, int dtype, int64_t outer, int64_t C, int64_t inner, int G, float eps,
+                                    void* q, float* scale_out, cudaStream_t s);
+cudaError_t launch_dequant_group_axis(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner, int G,
+                                      int out_dtype, void* y, cudaStream_t s);
 
 // ---- fused RMSNorm -> per-row quantize ----------------------------------------
 // x [rows, H] fp16 / bf16; gamma [H] of the same type or nullptr; q [rows, H] codes; scale_out [rows];

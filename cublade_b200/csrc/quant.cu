@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
                                                              float* __restrict__ amax) {
     constexpr int E = DTypeTraits<T>::kLanes;
     constexpr int kChunkPacks = kBlock * 4;
+    pdl_trigger();  // the cast kernel may take this CTA's place as soon as it leaves
     const int64_t npk = n / E;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
     const uint4* xp = reinterpret_cast<const uint4*>(x);
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
 template <typename T, bool PARTIALS>
 __global__ void __launch_bounds__(kBlock) amax_tensor_scalar_kernel(const T* __restrict__ x, int64_t n,
                                                                     float* __restrict__ amax) {
+    pdl_trigger();
     float m = 0.0f;
     for (int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (int64_t)gridDim.x * kBlock)
         m = fmaxf(m, fabsf(DTypeTraits<T>::to_float(x[i])));
@@ -130,21 +132,26 @@ __global__ void __launch_bounds__(kBlock) cast_tensor_kernel(const T* __restrict
     constexpr int E = DTypeTraits<T>::kLanes;
     constexpr int kChunkPacks = kBlock * 4;
     __shared__ float red_amax[kBlock / 32];
-    const InvScale is = inv_and_scale<Code>(fold_amax(amax, nparts, red_amax), eps);
-    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = is.scale;
     const int64_t npk = n / E;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
     const uint4* xp = reinterpret_cast<const uint4*>(x);
-    for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-        const int64_t p0 = c * kChunkPacks + threadIdx.x;
-        uint4 v[4];
-        bool ok[4];
+    // The first chunk's loads are issued BEFORE the wait on the amax kernel: x is an input nobody writes,
+    // so under a programmatic launch edge they overlap that kernel's tail; the amax itself is read after.
+    uint4 v[4];
+    bool ok[4];
+    int64_t c = blockIdx.x;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int64_t p = p0 + k * kBlock;
-            ok[k] = p < npk;
-            if (ok[k]) v[k] = ld_stream16(xp + p);
-        }
+    for (int k = 0; k < 4; ++k) {
+        const int64_t p = c * kChunkPacks + threadIdx.x + k * kBlock;
+        ok[k] = c < nchunks && p < npk;
+        if (ok[k]) v[k] = ld_stream16(xp + p);
+    }
+    pdl_wait();
+    pdl_trigger();  // a dequantize kernel behind this one may start its prologue
+    const InvScale is = inv_and_scale<Code>(fold_amax(amax, nparts, red_amax), eps);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = is.scale;
+    while (c < nchunks) {
+        const int64_t p0 = c * kChunkPacks + threadIdx.x;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             if (!ok[k]) continue;
@@ -152,6 +159,13 @@ __global__ void __launch_bounds__(kBlock) cast_tensor_kernel(const T* __restrict
             const uint2 codes = pack_encode<T, Code>(v[k], is.inv);
             if constexpr (E == 8) st_stream8(q + p * 8, codes);
             else st_stream4(q + p * 4, codes.x);
+        }
+        c += gridDim.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t p = c * kChunkPacks + threadIdx.x + k * kBlock;
+            ok[k] = c < nchunks && p < npk;
+            if (ok[k]) v[k] = ld_stream16(xp + p);
         }
     }
     if (blockIdx.x == 0) {
@@ -166,6 +180,8 @@ __global__ void __launch_bounds__(kBlock) cast_tensor_scalar_kernel(const T* __r
                                                                     float eps, uint8_t* __restrict__ q,
                                                                     float* __restrict__ scale_out) {
     __shared__ float red_amax[kBlock / 32];
+    pdl_wait();
+    pdl_trigger();
     const InvScale is = inv_and_scale<Code>(fold_amax(amax, nparts, red_amax), eps);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = is.scale;
     for (int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (int64_t)gridDim.x * kBlock)
@@ -185,6 +201,7 @@ __global__ void __launch_bounds__(BLOCK) quant_segments_kernel(const T* __restri
                                                                 float* __restrict__ scale_out) {
     constexpr int E = DTypeTraits<T>::kLanes;
     constexpr int kTeamsPerCta = BLOCK / TEAM;
+    pdl_trigger();  // a dequantize kernel queued behind this one may be set up while the last CTAs run
     const int t = threadIdx.x % TEAM;
     const int64_t seg = (int64_t)blockIdx.x * kTeamsPerCta + threadIdx.x / TEAM;
     const bool live = seg < nseg;
@@ -277,6 +294,8 @@ __global__ void __launch_bounds__(kBlock) dequant_kernel(const uint8_t* __restri
                                                          int64_t pps /* packs per segment, or shift */,
                                                          OutT* __restrict__ y) {
     constexpr int kChunkPacks = kBlock * 4;
+    pdl_wait();  // codes and scales may come from the kernel just before this one
+    pdl_trigger();
     const int64_t npk = n / 8;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
     const uint2* qp = reinterpret_cast<const uint2*>(q);
@@ -322,6 +341,8 @@ __global__ void __launch_bounds__(kBlock) dequant16_kernel(const uint8_t* __rest
                                                            int64_t pps /* 16-packs per segment, or shift */,
                                                            int64_t seg_len, OutT* __restrict__ y) {
     constexpr int kChunkPacks = kBlock * 4;
+    pdl_wait();  // codes and scales may come from the kernel just before this one
+    pdl_trigger();
     const int64_t npk = n / 16;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
     const uint4* qp = reinterpret_cast<const uint4*>(q);
@@ -364,6 +385,8 @@ template <typename OutT, typename Code>
 __global__ void __launch_bounds__(kBlock) dequant_scalar_kernel(const uint8_t* __restrict__ q,
                                                                 const float* __restrict__ scale, int64_t n,
                                                                 int64_t seg_len, OutT* __restrict__ y) {
+    pdl_wait();
+    pdl_trigger();
     for (int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (int64_t)gridDim.x * kBlock) {
         const float s = __ldg(scale + (seg_len > 0 ? i / seg_len : 0));
         y[i] = DTypeTraits<OutT>::from_float(__fmul_rn(Code::decode1(q[i]), s));
@@ -375,10 +398,14 @@ __global__ void __launch_bounds__(kBlock) dequant_scalar_kernel(const uint8_t* _
 // ===========================================================================
 static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// CTAs for a grid-stride loop over work_items chunks: at most ctas_per_sm resident CTAs per SM, and of the
+// grids with that many loop iterations the smallest, so every CTA gets the same number of chunks (+-1)
+// instead of a full wave followed by a partly filled one.
 static inline int persistent_grid(int64_t work_items, int ctas_per_sm) {
-    int64_t cap = (int64_t)sm_count() * ctas_per_sm;
-    int64_t g = work_items < cap ? work_items : cap;
-    return (int)(g < 1 ? 1 : g);
+    const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
+    if (work_items <= cap) return (int)(work_items < 1 ? 1 : work_items);
+    const int64_t iters = (work_items + cap - 1) / cap;
+    return (int)((work_items + iters - 1) / iters);
 }
 
 // grid of the amax kernel for n elements (= number of partial slots it writes in PARTIALS mode)
@@ -428,13 +455,12 @@ static cudaError_t cast_tensor_t(const void* x, int64_t n, const float* amax, in
     // the host layer never calls with n == 0, keep one CTA so scale_out is defined.
     if (aligned(x, 16) && aligned(q, 8)) {
         const int64_t nchunks = (n / E + kBlock * 4 - 1) / (kBlock * 4);
-        cast_tensor_kernel<T, Code><<<persistent_grid(nchunks, 8), kBlock, 0, s>>>(
-            static_cast<const T*>(x), n, amax, nparts, eps, static_cast<uint8_t*>(q), scale_out);
-    } else {
-        cast_tensor_scalar_kernel<T, Code><<<persistent_grid((n + kBlock - 1) / kBlock, 8), kBlock, 0, s>>>(
-            static_cast<const T*>(x), n, amax, nparts, eps, static_cast<uint8_t*>(q), scale_out);
+        return launch_dependent(cast_tensor_kernel<T, Code>, (unsigned)persistent_grid(nchunks, 8), kBlock, 0, s,
+                                static_cast<const T*>(x), n, amax, nparts, eps, static_cast<uint8_t*>(q), scale_out);
     }
-    return cudaPeekAtLastError();
+    return launch_dependent(cast_tensor_scalar_kernel<T, Code>, (unsigned)persistent_grid((n + kBlock - 1) / kBlock, 8),
+                            kBlock, 0, s, static_cast<const T*>(x), n, amax, nparts, eps, static_cast<uint8_t*>(q),
+                            scale_out);
 }
 
 cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float* amax, int nparts, float eps, int code,
@@ -529,7 +555,7 @@ static cudaError_t dequant_t(const void* q, const float* scale, int64_t n, int64
     const uint8_t* qp = static_cast<const uint8_t*>(q);
     OutT* yp = static_cast<OutT*>(y);
     if (!vec_ok) {
-        dequant_scalar_kernel<OutT, Code><<<persistent_grid((n + kBlock - 1) / kBlock, 8), kBlock, 0, s>>>(
+        launch_dependent(dequant_scalar_kernel<OutT, Code>, (unsigned)persistent_grid((n + kBlock - 1) / kBlock, 8), kBlock, 0, s, 
             qp, scale, n, seg_len, yp);
         return cudaPeekAtLastError();
     }
@@ -537,15 +563,15 @@ static cudaError_t dequant_t(const void* q, const float* scale, int64_t n, int64
         const int64_t nchunks16 = (n / 16 + kBlock * 4 - 1) / (kBlock * 4);
         const int grid16 = persistent_grid(nchunks16, 8);
         if (seg_len == 0) {
-            dequant16_kernel<OutT, Code, 0><<<grid16, kBlock, 0, s>>>(qp, scale, n, 0, 0, yp);
+            launch_dependent(dequant16_kernel<OutT, Code, 0>, (unsigned)grid16, kBlock, 0, s, qp, scale, n, 0, 0, yp);
         } else {
             const int64_t pps = seg_len / 16;
             if ((pps & (pps - 1)) == 0) {
                 int shift = 0;
                 while ((int64_t(1) << shift) < pps) ++shift;
-                dequant16_kernel<OutT, Code, 1><<<grid16, kBlock, 0, s>>>(qp, scale, n, shift, seg_len, yp);
+                launch_dependent(dequant16_kernel<OutT, Code, 1>, (unsigned)grid16, kBlock, 0, s, qp, scale, n, shift, seg_len, yp);
             } else {
-                dequant16_kernel<OutT, Code, 2><<<grid16, kBlock, 0, s>>>(qp, scale, n, pps, seg_len, yp);
+                launch_dependent(dequant16_kernel<OutT, Code, 2>, (unsigned)grid16, kBlock, 0, s, qp, scale, n, pps, seg_len, yp);
             }
         }
         return cudaPeekAtLastError();
@@ -553,15 +579,15 @@ static cudaError_t dequant_t(const void* q, const float* scale, int64_t n, int64
     const int64_t nchunks = (n / 8 + kBlock * 4 - 1) / (kBlock * 4);
     const int grid = persistent_grid(nchunks, 8);
     if (seg_len == 0) {
-        dequant_kernel<OutT, Code, 0><<<grid, kBlock, 0, s>>>(qp, scale, n, 0, yp);
+        launch_dependent(dequant_kernel<OutT, Code, 0>, (unsigned)grid, kBlock, 0, s, qp, scale, n, 0, yp);
     } else {
         const int64_t pps = seg_len / 8;
         if ((pps & (pps - 1)) == 0) {
             int shift = 0;
             while ((int64_t(1) << shift) < pps) ++shift;
-            dequant_kernel<OutT, Code, 1><<<grid, kBlock, 0, s>>>(qp, scale, n, shift, yp);
+            launch_dependent(dequant_kernel<OutT, Code, 1>, (unsigned)grid, kBlock, 0, s, qp, scale, n, shift, yp);
         } else {
-            dequant_kernel<OutT, Code, 2><<<grid, kBlock, 0, s>>>(qp, scale, n, pps, yp);
+            launch_dependent(dequant_kernel<OutT, Code, 2>, (unsigned)grid, kBlock, 0, s, qp, scale, n, pps, yp);
         }
     }
     return cudaPeekAtLastError();

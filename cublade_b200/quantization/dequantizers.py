@@ -8,6 +8,7 @@ from ..bindings.cuda.dequantize_fp8 import dequantize_per_tensor_fp8 as _fp8_ten
 from ..bindings.cuda.dequantize_int8 import (
     dequantize_per_axis_int8 as _int8_axis,
     dequantize_per_channel_int8 as _int8_channel,
+    dequantize_per_group_axis_int8 as _int8_group_axis,
     dequantize_per_group_int8 as _int8_group,
     dequantize_per_tensor_int8 as _int8_tensor,
 )
@@ -48,12 +49,16 @@ def dequantize_tensor(qt: QuantizedTensor) -> torch.Tensor:
         if qt.mode == "group":
             if qt.group_size is None:
                 raise ValueError("INT8 group dequant needs qt.group_size")
-            moved = qt.data.movedim(qt.axis, -1).contiguous()
-            lead, length = moved.shape[:-1], moved.shape[-1]
+            data = qt.data
+            axis, length = qt.axis % data.dim(), data.shape[qt.axis]
             if length % qt.group_size != 0:
                 raise ValueError(f"group_size {qt.group_size} must evenly divide axis length {length}")
-            y_rows = _int8_group(moved.view(-1, qt.group_size), qt.scale, qt.group_size, qt.original_dtype)
-            return y_rows.view(*lead, length).movedim(-1, qt.axis).contiguous()
+            if axis == data.dim() - 1:
+                return _int8_group(data.view(-1, qt.group_size), qt.scale, qt.group_size,
+                                   qt.original_dtype).view(data.shape)
+            # a non-last axis, dequantized where the codes lie (the reference moves the axis last with a copy and
+            # back with another, dequantizers.py:58-72)
+            return _int8_group_axis(data, qt.scale, axis, qt.group_size, qt.original_dtype)
         raise ValueError(f"Unsupported INT8 mode '{qt.mode}'")
 
     raise ValueError(f"No dequant kernel registered for dtype={qt.dtype}")

@@ -14,6 +14,7 @@ from ..bindings.cuda.quantize_fp8 import quantize_per_tensor_fp8 as _fp8_tensor
 from ..bindings.cuda.quantize_int8 import (
     quantize_per_axis_int8 as _int8_axis,
     quantize_per_channel_int8 as _int8_channel,
+    quantize_per_group_axis_int8 as _int8_group_axis,
     quantize_per_group_int8 as _int8_group,
     quantize_per_tensor_int8 as _int8_tensor,
 )
@@ -77,8 +78,9 @@ def quantize_tensor(
     * ``mode``: ``"tensor"`` one scale; ``"channel"`` one scale per index of ``ch_axis`` (the reference serves
       axis 0 only and raises ``NotImplementedError`` otherwise; here any axis is quantized in place, with the
       result of moving the axis to the front, quantizing and moving it back); ``"group"`` one scale per ``group_size`` consecutive elements
-      along ``ch_axis`` (which is moved last first; ``group_size`` must divide it, else ``ValueError``).
-      Group scales come back flat, ``(num_groups,)``, in the moved layout's order.
+      along ``ch_axis`` (``group_size`` must divide it, else ``ValueError``).  Group scales come back flat,
+      ``(num_groups,)``, in the order of the layout with ``ch_axis`` moved last, as in the reference -- which
+      gets there through two transposing copies; here a non-last axis is quantized where it lies.
     * an unregistered ``(mode, dtype)`` pair, a CPU / non-contiguous tensor or a wrong input dtype raise ``ValueError``.
 
     Returns a ``QuantizedTensor`` whose ``zero_point`` is a 0-d float32 zero.
@@ -104,12 +106,19 @@ def quantize_tensor(
                 raise ValueError(f"quantize_tensor: ch_axis {ch_axis} out of range for a {x.dim()}-d tensor")
             q, scale = _int8_axis(x, ch_axis, eps)
     elif mode == "group":
-        moved = x.movedim(ch_axis, -1).contiguous()
-        lead, length = moved.shape[:-1], moved.shape[-1]
+        if not -x.dim() <= ch_axis < x.dim():
+            raise IndexError(f"Dimension out of range (expected to be in range of [{-x.dim()}, {x.dim() - 1}], "
+                             f"but got {ch_axis})")
+        axis, length = ch_axis % x.dim(), x.shape[ch_axis]
         if length % group_size != 0:
             raise ValueError(f"group_size {group_size} must evenly divide axis length {length}")
-        q_rows, scale = kernel(moved.view(-1, group_size), group_size, eps)
-        q = q_rows.view(*lead, length).movedim(-1, ch_axis).contiguous()
+        if axis == x.dim() - 1:  # groups are contiguous runs already
+            q_rows, scale = kernel(x.view(-1, group_size), group_size, eps)
+            q = q_rows.view(x.shape)
+        else:
+            # the reference copies the axis last, quantizes rows and copies the codes back (quantizers.py:122-132);
+            # same codes and scales, same scale order, computed where the data lies
+            q, scale = _int8_group_axis(x, axis, group_size, eps)
     else:  # unreachable: the registry lookup above already rejected unknown modes
         raise ValueError(f"Unsupported mode '{mode}'; expected tensor / channel / group")
 

@@ -222,6 +222,23 @@ int32_t cb_dequantize_per_axis_int8(const void* q, const float* scale, int64_t o
                                     int32_t out_dtype, void* y, void* stream);
 
 /* ------------------------------------------------------------------------
+ * INT8 per-group with the groups along a NON-LAST axis, in place: x contiguous, viewed as
+ * [outer, C, inner]; group_size consecutive indices of C form a group at every (outer, inner)
+ * position; group_size in (0, 4096] must divide C.  Same arithmetic per group as
+ * cb_quantize_per_group_int8 and the same scale order as the reference's route
+ *   cublade/quantization/quantizers.py:122-132 (movedim(ch_axis, -1).contiguous().view(-1, G), kernel,
+ *   view back, movedim(-1, ch_axis).contiguous()), cublade/quantization/dequantizers.py:58-72
+ * i.e. scale fp32[outer * inner * C / group_size] with index (o * inner + i) * (C / group_size) + c / group_size,
+ * so codes, scales and dequantized values equal that route's bit for bit -- without its two
+ * transposing copies (3 bytes of HBM traffic per element instead of 9).  No alignment requirement
+ * (vector kernels when inner is a multiple of the 16-byte lane count and x is 16-byte aligned).
+ * ------------------------------------------------------------------------ */
+int32_t cb_quantize_per_group_axis_int8(const void* x, int32_t dtype, int64_t outer, int64_t C, int64_t inner,
+                                        int64_t group_size, float eps, void* q, float* scale, void* stream);
+int32_t cb_dequantize_per_group_axis_int8(const void* q, const float* scale, int64_t outer, int64_t C, int64_t inner,
+                                          int64_t group_size, int32_t out_dtype, void* y, void* stream);
+
+/* ------------------------------------------------------------------------
  * Fused RMSNorm -> per-row (per-token) quantize: one pass over x, 3 bytes of HBM traffic per
  * element instead of the 7 of "RMSNorm kernel, then per-channel quantize kernel".
  * The reference announces the op (README.md:20, "upcoming RMSNorm-fused-quant work" for which its

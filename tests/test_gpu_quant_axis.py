@@ -79,3 +79,66 @@ def test_full_size_last_axis_equals_transposed_axis0_path_on_the_gpu():
     assert torch.equal(s, st) and torch.equal(q, qt.t())
     y = dequantize_per_axis_int8(q, s, 1)
     assert ((y.float() - x.float()).abs() <= 0.5 * s[None, :] + x.float().abs() * 2.0 ** -8 + 1e-30).all()
+
+
+# ------------------------------------------------------------------------------------------------
+# per-GROUP along a non-last axis, quantized where the data lies (the reference copies the axis last
+# and back: cublade/quantization/quantizers.py:122-132, dequantizers.py:58-72)
+# ------------------------------------------------------------------------------------------------
+GROUP_CASES = [
+    # shape, axis, group size          kernel the launcher picks
+    ((256, 64), 0, 32),              # vector: inner = 64
+    ((4, 128, 24), 1, 32),           # vector, inner = 24 (3 bf16 packs)
+    ((2, 96, 5, 8), 1, 16),          # vector, inner = 40
+    ((3, 64, 6), 1, 64),             # scalar for 16-bit (inner = 6), one group per column
+    ((8, 10, 7), 1, 5),              # scalar, odd sizes
+    ((512, 128), 0, 128),            # vector, tall groups
+    ((6, 4096, 16), 1, 4096),        # the largest group the reference accepts
+    ((40, 12), 0, 1),                # group of one element
+    ((2, 3, 64, 4), 2, 8),           # fp32 packs of 4 fit inner = 4; 16-bit scalar
+    ((5, 32, 64), -2, 32),           # negative axis
+]
+
+
+@pytest.mark.parametrize("shape,axis,G", GROUP_CASES, ids=[f"{s}-ax{a}-g{g}" for s, a, g in GROUP_CASES])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_group_mode_along_a_non_last_axis_without_copies(shape, axis, G, dtype):
+    import cublade_b200 as cb
+
+    g = torch.Generator().manual_seed(abs(hash((shape, axis, G))) % (2 ** 31))
+    x = (torch.randn(*shape, generator=g) * 1.3).to(dtype)
+    idx = [slice(None)] * len(shape)
+    idx[axis] = slice(0, G)
+    x[tuple(idx)] *= 23.0                      # first group of every line: another range
+    x.view(-1)[:: max(1, x.numel() // 7)] = 0  # some exact zeros
+    if x.shape[axis] >= 2 * G:
+        idx[axis] = slice(G, 2 * G)
+        x[tuple(idx)] = 0                      # all-zero groups: scale = 1 / (127 / eps)
+    ref = O.quantize_tensor(x, torch.int8, "group", group_size=G, ch_axis=axis)
+    qt = cb.quantize_tensor(x.cuda(), dtype=torch.int8, mode="group", group_size=G, ch_axis=axis)
+    assert qt.data.shape == x.shape and qt.data.is_contiguous() and qt.scale.shape == (x.numel() // G,)
+    assert qt.axis == axis and qt.group_size == G
+    assert_bits_equal(qt.scale, ref["scale"], "scales")
+    assert_bits_equal(qt.data, ref["data"], "codes")
+    if dtype == torch.float32:
+        with pytest.raises(ValueError):
+            cb.dequantize_tensor(qt)  # float32 origin cannot come back, as in the reference
+        qt.original_dtype = ref["original_dtype"] = torch.float16
+    assert_bits_equal(cb.dequantize_tensor(qt), O.dequantize_tensor(ref), "dequant")
+
+
+def test_group_mode_non_last_axis_full_size_against_the_copying_route():
+    """bf16 [8192, 8192] with groups of 128 down the rows (axis 0): codes, scales and dequantized values must equal
+    what the library's contiguous-group kernels give on the transposed copy -- the route the reference takes."""
+    import cublade_b200 as cb
+
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    x = (torch.randn(8192, 8192, generator=gen, device="cuda") * 0.5).to(torch.bfloat16)
+    qt = cb.quantize_tensor(x, dtype=torch.int8, mode="group", group_size=128, ch_axis=0)
+    moved = x.t().contiguous()
+    want = cb.quantize_tensor(moved, dtype=torch.int8, mode="group", group_size=128, ch_axis=-1)
+    assert torch.equal(qt.scale, want.scale)
+    assert torch.equal(qt.data, want.data.t())
+    assert torch.equal(cb.dequantize_tensor(qt), cb.dequantize_tensor(want).t())
+    with pytest.raises(ValueError, match="evenly divide"):
+        cb.quantize_tensor(x, dtype=torch.int8, mode="group", group_size=96, ch_axis=0)

@@ -130,10 +130,12 @@ def test_llm_int8_outlier_split(M, n_out):
     y = layer(x.cuda())
     _check(y, O.w8a16_forward(x, ref_layer, bias), "outlier split vs reference rounding order")
     _check(y, O.w8a16_forward_fp64(x, ref_layer, bias), "outlier split vs exact")
-    # and the split matters: without it the same input loses accuracy
-    plain = O.w8a16_quantize(w32, torch.bfloat16)
-    assert rel_fro(O.w8a16_forward_fp64(x, plain, bias), x.double() @ w32.double().t() + bias.double()) > \
-        rel_fro(y, x.double() @ w32.double().t() + bias.double())
+    # and the split matters: the same kernels without it lose accuracy on the same input
+    plain = cb.cuBladeW8A16LinearLayer(K, N, bias=True, dtype=torch.bfloat16)
+    plain.quantize(w32)
+    plain.bias = torch.nn.Parameter(bias)
+    exact = x.double() @ w32.double().t() + bias.double()
+    assert rel_fro(plain.cuda()(x.cuda()), exact) > rel_fro(y, exact)
 
 
 def test_strided_rows_batched_input_and_state_dict():

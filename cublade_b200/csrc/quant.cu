@@ -58,7 +58,11 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
                                                              float* __restrict__ amax) {
     constexpr int E = DTypeTraits<T>::kLanes;
     constexpr int kChunkPacks = kBlock * 4;
-    pdl_trigger();  // the cast kernel may take this CTA's place as soon as it leaves
+    // Launched with a programmatic edge: this CTA may be resident before the kernel ahead of it in the stream (which
+    // may have produced x) has finished, so it waits for that kernel first; the cast kernel behind it may then be
+    // set up in turn and takes this CTA's place as soon as it leaves.
+    pdl_wait();
+    pdl_trigger();
     const int64_t npk = n / E;
     const int64_t nchunks = (npk + kChunkPacks - 1) / kChunkPacks;
     const uint4* xp = reinterpret_cast<const uint4*>(x);
@@ -101,6 +105,7 @@ __global__ void __launch_bounds__(kBlock) amax_tensor_kernel(const T* __restrict
 template <typename T, bool PARTIALS>
 __global__ void __launch_bounds__(kBlock) amax_tensor_scalar_kernel(const T* __restrict__ x, int64_t n,
                                                                     float* __restrict__ amax) {
+    pdl_wait();
     pdl_trigger();
     float m = 0.0f;
     for (int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += (int64_t)gridDim.x * kBlock)
@@ -422,9 +427,11 @@ static cudaError_t amax_tensor_t(const void* x, int64_t n, float* amax, int* npa
     if (n <= 0) return cudaSuccess;
     const int grid = amax_grid<T>(x, n);
     if (nparts) *nparts = grid;
-    if (aligned(x, 16)) amax_tensor_kernel<T, PARTIALS><<<grid, kBlock, 0, s>>>(static_cast<const T*>(x), n, amax);
-    else amax_tensor_scalar_kernel<T, PARTIALS><<<grid, kBlock, 0, s>>>(static_cast<const T*>(x), n, amax);
-    return cudaPeekAtLastError();
+    if (aligned(x, 16))
+        return launch_dependent(amax_tensor_kernel<T, PARTIALS>, (unsigned)grid, kBlock, 0, s, static_cast<const T*>(x), n,
+                                amax);
+    return launch_dependent(amax_tensor_scalar_kernel<T, PARTIALS>, (unsigned)grid, kBlock, 0, s, static_cast<const T*>(x),
+                            n, amax);
 }
 
 cudaError_t launch_amax_tensor(const void* x, int dtype, int64_t n, float* amax, cudaStream_t s) {

@@ -10,9 +10,9 @@
 // moved layout [outer, inner, C / G]: scale[(o * inner + i) * (C / G) + c / G].
 //
 // Layout of the work: a group is G elements `inner` apart, so a thread takes the same 16-byte pack
-// (8 or 4 neighbours along `inner`) of each of the G rows of a group: its lanes belong to 8 (4)
-// DIFFERENT groups, adjacent threads read adjacent packs (coalesced), and every lane keeps its own
-// running maximum, reciprocal and scale.  The second read of the G packs comes from L2.
+// (8 or 4 neighbours along `inner`) of rows of a group: its lanes belong to 8 (4) DIFFERENT groups,
+// adjacent threads read adjacent packs (coalesced), and every lane keeps its own running maximum,
+// reciprocal and scale.  The second read of the packs comes from L2.
 #include "launch.h"
 #include "pack.cuh"
 
@@ -64,7 +64,13 @@ struct LaneAbsMax<__half> : LaneAbsMax16<__half, __half2> {};
 template <>
 struct LaneAbsMax<__nv_bfloat16> : LaneAbsMax16<__nv_bfloat16, __nv_bfloat162> {};
 
-// x viewed as packs: [outer, C, ppr] packs, ppr = inner / E.  One work item = (o, group cg, pack ip).
+// x viewed as packs: [outer, C, ppr] packs, ppr = inner / E.  One work item = (o, group cg, pack ip); a CTA of
+// kWarps warps takes 32 consecutive items -- lane = item, so a warp's loads of one row are 32 adjacent packs -- and
+// warp w takes rows w, w + kWarps, ... of the groups (four loads in flight per thread).  The per-lane maxima of the
+// warps meet in shared memory; every thread then derives its items' reciprocals and encodes its own rows again
+// (second read served by L2).
+constexpr int kWarps = kBlock / 32;
+
 template <typename T>
 __global__ void __launch_bounds__(kBlock) quant_group_axis_kernel(const T* __restrict__ x, int64_t items, int64_t C,
                                                                   int64_t ppr, int G, float eps,
@@ -72,40 +78,51 @@ __global__ void __launch_bounds__(kBlock) quant_group_axis_kernel(const T* __res
                                                                   float* __restrict__ scale_out) {
     constexpr int E = DTypeTraits<T>::kLanes;
     pdl_trigger();
+    __shared__ float red[kWarps][E][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t ngr = C / G, inner = ppr * E;
     const uint4* xp = reinterpret_cast<const uint4*>(x);
-    for (int64_t w = (int64_t)blockIdx.x * kBlock + threadIdx.x; w < items; w += (int64_t)gridDim.x * kBlock) {
-        const int64_t ip = w % ppr, og = w / ppr, cg = og % ngr, o = og / ngr;
-        const int64_t pack0 = (o * C + cg * G) * ppr + ip;  // pack of row j of the group: pack0 + j * ppr
-        LaneAbsMax<T> am;
-        int j = 0;
-        for (; j + 4 <= G; j += 4) {
-            const uint4 v0 = ld_keep16(xp + pack0 + (int64_t)(j + 0) * ppr);
-            const uint4 v1 = ld_keep16(xp + pack0 + (int64_t)(j + 1) * ppr);
-            const uint4 v2 = ld_keep16(xp + pack0 + (int64_t)(j + 2) * ppr);
-            const uint4 v3 = ld_keep16(xp + pack0 + (int64_t)(j + 3) * ppr);
+    const int64_t w = (int64_t)blockIdx.x * 32 + lane;
+    const bool live = w < items;
+    const int64_t ip = live ? w % ppr : 0, og = live ? w / ppr : 0, cg = og % ngr, o = og / ngr;
+    const int64_t pack0 = (o * C + cg * G) * ppr + ip;  // pack of row j of the group: pack0 + j * ppr
+    LaneAbsMax<T> am;
+    if (live) {
+        int j = warp;
+        for (; j + 3 * kWarps < G; j += 4 * kWarps) {
+            const uint4 v0 = ld_keep16(xp + pack0 + (int64_t)(j + 0 * kWarps) * ppr);
+            const uint4 v1 = ld_keep16(xp + pack0 + (int64_t)(j + 1 * kWarps) * ppr);
+            const uint4 v2 = ld_keep16(xp + pack0 + (int64_t)(j + 2 * kWarps) * ppr);
+            const uint4 v3 = ld_keep16(xp + pack0 + (int64_t)(j + 3 * kWarps) * ppr);
             am.update(v0); am.update(v1); am.update(v2); am.update(v3);
         }
-        for (; j < G; ++j) am.update(ld_keep16(xp + pack0 + (int64_t)j * ppr));
-        float amax[E], inv[E];
-        am.finish(amax);
-        const int64_t s0 = (o * inner + ip * E) * ngr + cg;  // lane l: + l * ngr
+        for (; j < G; j += kWarps) am.update(ld_keep16(xp + pack0 + (int64_t)j * ppr));
+    }
+    float amax[E], inv[E];
+    am.finish(amax);
 #pragma unroll
-        for (int l = 0; l < E; ++l) {
-            const InvScale is = inv_and_scale<Int8Code>(amax[l], eps);
-            inv[l] = is.inv;
-            scale_out[s0 + (int64_t)l * ngr] = is.scale;
-        }
-        for (j = 0; j < G; ++j) {
-            const int64_t p = pack0 + (int64_t)j * ppr;
-            float f[E];
-            pack_to_floats<T>(ld_stream16(xp + p), f);
+    for (int l = 0; l < E; ++l) red[warp][l][lane] = amax[l];
+    __syncthreads();
 #pragma unroll
-            for (int l = 0; l < E; ++l) f[l] = __fmul_rn(f[l], inv[l]);
-            const uint32_t lo = Int8Code::encode4(f[0], f[1], f[2], f[3]);
-            if constexpr (E == 8) st_stream8(q + p * 8, make_uint2(lo, Int8Code::encode4(f[4], f[5], f[6], f[7])));
-            else st_stream4(q + p * 4, lo);
-        }
+    for (int l = 0; l < E; ++l) {
+        float m = red[0][l][lane];
+#pragma unroll
+        for (int k = 1; k < kWarps; ++k) m = fmaxf(m, red[k][l][lane]);
+        const InvScale is = inv_and_scale<Int8Code>(m, eps);
+        inv[l] = is.inv;
+        // lane l of item (o, cg, ip) is position i = ip * E + l of the inner axis
+        if (live && warp == (l % kWarps)) scale_out[(o * inner + ip * E + l) * ngr + cg] = is.scale;
+    }
+    if (!live) return;
+    for (int j = warp; j < G; j += kWarps) {
+        const int64_t p = pack0 + (int64_t)j * ppr;
+        float f[E];
+        pack_to_floats<T>(ld_stream16(xp + p), f);
+#pragma unroll
+        for (int l = 0; l < E; ++l) f[l] = __fmul_rn(f[l], inv[l]);
+        const uint32_t lo = Int8Code::encode4(f[0], f[1], f[2], f[3]);
+        if constexpr (E == 8) st_stream8(q + p * 8, make_uint2(lo, Int8Code::encode4(f[4], f[5], f[6], f[7])));
+        else st_stream4(q + p * 4, lo);
     }
 }
 
@@ -131,40 +148,68 @@ __global__ void __launch_bounds__(kBlock) quant_group_axis_scalar_kernel(const T
     }
 }
 
-// y[o, c, i] = float(q[o, c, i]) * scale[(o * inner + i) * (C / G) + c / G]; VEC: 8 codes along inner per thread
-template <typename OutT, bool VEC>
+// y[o, c, i] = float(q[o, c, i]) * scale[(o * inner + i) * (C / G) + c / G].
+// Vector form: the work item of the quantizer -- (o, group, pack of 8 positions along inner), lane = item, warp w
+// takes rows w, w + kWarps, ... -- so the eight scales of an item (C / G floats apart) are fetched once per thread
+// and reused for all its rows.
+template <typename OutT>
 __global__ void __launch_bounds__(kBlock) dequant_group_axis_kernel(const uint8_t* __restrict__ q,
-                                                                    const float* __restrict__ scale, int64_t n,
-                                                                    int64_t C, int64_t inner, int G,
+                                                                    const float* __restrict__ scale, int64_t items,
+                                                                    int64_t C, int64_t ppr, int G,
                                                                     OutT* __restrict__ y) {
     pdl_wait();
     pdl_trigger();
-    const int64_t ngr = C / G;
-    if constexpr (VEC) {
-        const int64_t npk = n / 8;
-        for (int64_t p = (int64_t)blockIdx.x * kBlock + threadIdx.x; p < npk; p += (int64_t)gridDim.x * kBlock) {
-            const int64_t e0 = p * 8, i0 = e0 % inner, oc = e0 / inner, c = oc % C, o = oc / C;
-            const float* sp = scale + (o * inner + i0) * ngr + c / G;
-            float s[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t w = (int64_t)blockIdx.x * 32 + lane;
+    if (w >= items || warp >= G) return;
+    const int64_t ngr = C / G, inner = ppr * 8;
+    const int64_t ip = w % ppr, og = w / ppr, cg = og % ngr, o = og / ngr;
+    const int64_t pack0 = (o * C + cg * G) * ppr + ip;
+    const float* sp = scale + (o * inner + ip * 8) * ngr + cg;
+    float s[8];
 #pragma unroll
-            for (int l = 0; l < 8; ++l) s[l] = __ldg(sp + (int64_t)l * ngr);
-            const uint2 codes = ld_stream8(q + e0);
-            float a[4], b[4];
-            Int8Code::decode4(codes.x, a);
-            Int8Code::decode4(codes.y, b);
-            uint4 out;
-            out.x = DTypeTraits<OutT>::float2_to_word(__fmul_rn(a[0], s[0]), __fmul_rn(a[1], s[1]));
-            out.y = DTypeTraits<OutT>::float2_to_word(__fmul_rn(a[2], s[2]), __fmul_rn(a[3], s[3]));
-            out.z = DTypeTraits<OutT>::float2_to_word(__fmul_rn(b[0], s[4]), __fmul_rn(b[1], s[5]));
-            out.w = DTypeTraits<OutT>::float2_to_word(__fmul_rn(b[2], s[6]), __fmul_rn(b[3], s[7]));
-            st_stream16(reinterpret_cast<uint4*>(y) + p, out);
-        }
-    } else {
-        for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < n; e += (int64_t)gridDim.x * kBlock) {
-            const int64_t i = e % inner, oc = e / inner, c = oc % C, o = oc / C;
-            const float s = __ldg(scale + (o * inner + i) * ngr + c / G);
-            y[e] = DTypeTraits<OutT>::from_float(__fmul_rn(Int8Code::decode1(q[e]), s));
-        }
+    for (int l = 0; l < 8; ++l) s[l] = __ldg(sp + (int64_t)l * ngr);
+    const uint2* qp = reinterpret_cast<const uint2*>(q);
+    uint4* yp = reinterpret_cast<uint4*>(y);
+    auto decode = [&](const uint2& codes) {
+        float a[4], b[4];
+        Int8Code::decode4(codes.x, a);
+        Int8Code::decode4(codes.y, b);
+        uint4 out;
+        out.x = DTypeTraits<OutT>::float2_to_word(__fmul_rn(a[0], s[0]), __fmul_rn(a[1], s[1]));
+        out.y = DTypeTraits<OutT>::float2_to_word(__fmul_rn(a[2], s[2]), __fmul_rn(a[3], s[3]));
+        out.z = DTypeTraits<OutT>::float2_to_word(__fmul_rn(b[0], s[4]), __fmul_rn(b[1], s[5]));
+        out.w = DTypeTraits<OutT>::float2_to_word(__fmul_rn(b[2], s[6]), __fmul_rn(b[3], s[7]));
+        return out;
+    };
+    int j = warp;
+    for (; j + 3 * kWarps < G; j += 4 * kWarps) {
+        const int64_t p0 = pack0 + (int64_t)(j + 0 * kWarps) * ppr, p1 = pack0 + (int64_t)(j + 1 * kWarps) * ppr;
+        const int64_t p2 = pack0 + (int64_t)(j + 2 * kWarps) * ppr, p3 = pack0 + (int64_t)(j + 3 * kWarps) * ppr;
+        const uint2 c0 = ld_stream8(qp + p0), c1 = ld_stream8(qp + p1), c2 = ld_stream8(qp + p2), c3 = ld_stream8(qp + p3);
+        st_stream16(yp + p0, decode(c0));
+        st_stream16(yp + p1, decode(c1));
+        st_stream16(yp + p2, decode(c2));
+        st_stream16(yp + p3, decode(c3));
+    }
+    for (; j < G; j += kWarps) {
+        const int64_t p = pack0 + (int64_t)j * ppr;
+        st_stream16(yp + p, decode(ld_stream8(qp + p)));
+    }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kBlock) dequant_group_axis_scalar_kernel(const uint8_t* __restrict__ q,
+                                                                           const float* __restrict__ scale, int64_t n,
+                                                                           int64_t C, int64_t inner, int G,
+                                                                           OutT* __restrict__ y) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t ngr = C / G;
+    for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < n; e += (int64_t)gridDim.x * kBlock) {
+        const int64_t i = e % inner, oc = e / inner, c = oc % C, o = oc / C;
+        const float s = __ldg(scale + (o * inner + i) * ngr + c / G);
+        y[e] = DTypeTraits<OutT>::from_float(__fmul_rn(Int8Code::decode1(q[e]), s));
     }
 }
 
@@ -186,7 +231,9 @@ cudaError_t quant_t(const void* xv, int64_t outer, int64_t C, int64_t inner, int
     if (outer * C * inner <= 0) return cudaSuccess;
     if (inner % E == 0 && aligned_to(x, 16) && aligned_to(q, E == 8 ? 8 : 4)) {
         const int64_t ppr = inner / E, items = outer * (C / G) * ppr;
-        quant_group_axis_kernel<T><<<grid_for(items, 8), kBlock, 0, s>>>(x, items, C, ppr, G, eps, q, scale_out);
+        const int64_t ctas = (items + 31) / 32;
+        if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+        quant_group_axis_kernel<T><<<(unsigned)ctas, kBlock, 0, s>>>(x, items, C, ppr, G, eps, q, scale_out);
     } else {
         const int64_t items = outer * (C / G) * inner;
         quant_group_axis_scalar_kernel<T><<<grid_for(items, 8), kBlock, 0, s>>>(x, items, C, inner, G, eps, q, scale_out);
@@ -201,10 +248,13 @@ cudaError_t dequant_t(const void* qv, const float* scale, int64_t outer, int64_t
     OutT* y = static_cast<OutT*>(yv);
     const int64_t n = outer * C * inner;
     if (n <= 0) return cudaSuccess;
-    if (inner % 8 == 0 && aligned_to(q, 8) && aligned_to(y, 16))
-        return launch_dependent(dequant_group_axis_kernel<OutT, true>, grid_for(n / 8, 8), kBlock, 0, s, q, scale, n, C,
-                                inner, G, y);
-    return launch_dependent(dequant_group_axis_kernel<OutT, false>, grid_for(n, 8), kBlock, 0, s, q, scale, n, C, inner,
+    if (inner % 8 == 0 && aligned_to(q, 8) && aligned_to(y, 16)) {
+        const int64_t ppr = inner / 8, items = outer * (C / G) * ppr, ctas = (items + 31) / 32;
+        if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+        return launch_dependent(dequant_group_axis_kernel<OutT>, (unsigned)ctas, kBlock, 0, s, q, scale, items, C, ppr, G,
+                                y);
+    }
+    return launch_dependent(dequant_group_axis_scalar_kernel<OutT>, grid_for(n, 8), kBlock, 0, s, q, scale, n, C, inner,
                             G, y);
 }
 

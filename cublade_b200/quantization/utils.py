@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional, Type
 
+import torch
 import torch.nn as nn
 
 __all__ = ["replace_linear_layers"]
@@ -21,8 +22,8 @@ def replace_linear_layers(
     Selection is by substring of the dotted module path: a layer is skipped when any entry
     of ``exclude_modules`` occurs in its path, or when ``target_modules`` is given and none
     of its entries occurs.  The replacement is constructed as
-    ``target_class(in_features, out_features, bias=<had bias>, dtype=<weight dtype>, **quant_kwargs)``,
-    attached first, then asked to ``quantize(old_weight)``; the original bias ``Parameter``
+    ``target_class(in_features, out_features, bias=<had bias>, dtype=<weight dtype>, **quant_kwargs)``
+    on the device of the layer it replaces, attached first, then asked to ``quantize(old_weight)``; the original bias ``Parameter``
     object is re-attached afterwards.
     """
     quant_kwargs = quant_kwargs or {}
@@ -39,8 +40,12 @@ def replace_linear_layers(
         if target_modules is not None and not any(pat in path for pat in target_modules):
             continue
         weight, bias = child.weight, child.bias
-        replacement = target_class(child.in_features, child.out_features, bias=bias is not None,
-                                   dtype=weight.dtype, **quant_kwargs)
+        # the replacement's buffers are created where the weight lives, so the codes of a GPU-resident model
+        # stay on the GPU (created on the CPU, as the reference does, every layer's codes would cross PCIe
+        # twice: back to the host here and up again on the first forward)
+        with torch.device(weight.device):
+            replacement = target_class(child.in_features, child.out_features, bias=bias is not None,
+                                       dtype=weight.dtype, **quant_kwargs)
         setattr(module, name, replacement)
         getattr(module, name).quantize(weight)
         if bias is not None:

@@ -102,8 +102,9 @@ def quantize_model_sharded(model: nn.Module, rank: int, world_size: int, quant_t
             if target_modules is not None and not any(pat in path for pat in target_modules):
                 continue
             start, stop = shard_range(child.out_features, rank, world_size)
-            new = layer_cls(child.in_features, stop - start, bias=child.bias is not None, dtype=child.weight.dtype,
-                            **quant_kwargs)
+            with torch.device(child.weight.device):  # buffers live where the weight does
+                new = layer_cls(child.in_features, stop - start, bias=child.bias is not None, dtype=child.weight.dtype,
+                                **quant_kwargs)
             setattr(module, name, new)
             new.quantize(child.weight.detach()[start:stop])
             if child.bias is not None:
@@ -114,11 +115,27 @@ def quantize_model_sharded(model: nn.Module, rank: int, world_size: int, quant_t
     return model
 
 
-def all_gather_columns(y_local: torch.Tensor, group=None) -> torch.Tensor:
-    """Concatenate the ranks' output-feature slices along the last dim (equal slice widths)."""
+def all_gather_columns(y_local: torch.Tensor, group=None, out_features: Optional[int] = None) -> torch.Tensor:
+    """Concatenate the ranks' output-feature slices along the last dim.
+
+    The slices of ``shard_range`` differ by one column when ``out_features`` is not a multiple of the world size;
+    pass the unsharded ``out_features`` then (each rank's width follows from it).  Without it every rank must hold
+    the same width, which is checked."""
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
-    parts = [torch.empty_like(y_local) for _ in range(world)]
-    dist.all_gather(parts, y_local.contiguous(), group=group)
-    return torch.cat(parts, dim=-1)
+    if out_features is None:
+        widths = torch.tensor([y_local.shape[-1]], dtype=torch.int64, device=y_local.device)
+        all_w = [torch.empty_like(widths) for _ in range(world)]
+        dist.all_gather(all_w, widths, group=group)
+        widths = [int(w.item()) for w in all_w]
+    else:
+        widths = [(lambda r: r[1] - r[0])(shard_range(out_features, r, world)) for r in range(world)]
+    widest = max(widths)
+    mine = y_local.contiguous()
+    if mine.shape[-1] != widest:  # pad to the widest slice: all_gather wants equal shapes
+        pad = torch.zeros(*mine.shape[:-1], widest - mine.shape[-1], dtype=mine.dtype, device=mine.device)
+        mine = torch.cat([mine, pad], dim=-1)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine, group=group)
+    return torch.cat([p[..., :w] for p, w in zip(parts, widths)], dim=-1)

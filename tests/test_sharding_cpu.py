@@ -69,6 +69,14 @@ def _worker(rank, world, port, out):
             ok_scale = qt.scale.view(torch.int32).item() == s_ref.view(torch.int32).item()
             ok_codes = torch.equal(qt.data.view(torch.uint8), q_ref[a:b].contiguous().view(torch.uint8))
             out.put((rank, str(dtype), ok_scale, ok_codes, qt.mode, qt.original_dtype == x.dtype))
+        # column slices of unequal width (7 output features over 2 ranks: 4 + 3) gather back in order
+        from cublade_b200.sharding import all_gather_columns
+
+        y = torch.arange(3 * 7, dtype=torch.float32).reshape(3, 7)
+        n0, n1 = shard_range(7, rank, world)
+        ok_a = torch.equal(all_gather_columns(y[:, n0:n1], out_features=7), y)
+        ok_b = torch.equal(all_gather_columns(y[:, n0:n1]), y)  # widths exchanged when out_features is not given
+        out.put((rank, "all_gather_columns", ok_a, ok_b, "tensor", True))
     finally:
         dist.destroy_process_group()
 
@@ -80,11 +88,11 @@ def test_sharded_per_tensor_quantization_equals_single_rank_bit_for_bit():
     procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [out.get(timeout=120) for _ in range(world * 2)]
+    results = [out.get(timeout=120) for _ in range(world * 3)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert len(results) == 4
+    assert len(results) == 6
     for rank, dtype, ok_scale, ok_codes, mode, ok_dtype in results:
         assert ok_scale and ok_codes and mode == "tensor" and ok_dtype, (rank, dtype)
 

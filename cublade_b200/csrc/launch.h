@@ -107,6 +107,10 @@ struct W8A16Args {
     int act_dtype;        // kBF16 or kF16
     void* workspace;      // may be nullptr when workspace_bytes == 0
     size_t workspace_bytes;
+    // The kernels are launched with a programmatic edge to the kernel ahead of them in the stream and fetch their
+    // first weights before they wait for it: legal only when that kernel did not write wq (true for a layer's own
+    // weights; false when wq was unpacked from 4-bit codes by the launch just before).
+    bool weights_ready = true;
 };
 size_t w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 // path: 0 = automatic, 1 = weight-streaming (skinny M) kernel, 2 = tcgen05 CTA-pair GEMM, 3 = tcgen05 single-CTA GEMM

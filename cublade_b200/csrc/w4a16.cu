@@ -353,6 +353,7 @@ cudaError_t launch_w4a16(const W4A16Args& a, cudaStream_t s, int* launches) {
     w.workspace = static_cast<char*>(a.workspace) + codes;
     w.workspace_bytes = a.workspace_bytes - codes;
     *launches = 2;
+    w.weights_ready = false;  // the unpack kernel above has just written them
     return launch_w8a16(w, 0, s);
 }
 

@@ -110,6 +110,7 @@ struct StreamParams {
     void* y;
     int64_t ldy;
     int64_t m0;  // first activation row of this pass
+    int weights_ready;  // 1: the first stage of weights may be fetched before waiting for the kernel ahead
 };
 
 // One 16-byte (VEC==16) / 8 / 4 / 1-byte-granular load of weight codes for row `r`, k in [k, k+VEC').
@@ -254,6 +255,9 @@ __global__ void __launch_bounds__(kWarps * 32) w8a16_stream_kernel(const StreamP
         Stage st0, st1;
         int64_t r = (int64_t)warp * U;
         const int64_t step = (int64_t)kWarps * U;
+        // this variant's stages hold activations as well, so it waits for the kernel ahead before its first load
+        pdl_wait();
+        pdl_trigger();
         load_stage(st0, r);
         while (r < nrounds) {
             load_stage(st1, r + step);
@@ -425,7 +429,17 @@ __global__ void __launch_bounds__(kWarps * 32, 7) w8a16_stream_fast_kernel(const
         Stage st0, st1;
         int r = warp * U;
         constexpr int step = kWarps * U;
-        load_stage(st0, r);
+        // Programmatic launch edge: the first stage of weights is requested before the wait for the kernel ahead
+        // (which may still be producing the activations), so the stream ramps up under that kernel's tail.
+        if (p.weights_ready) {
+            pdl_trigger();
+            load_stage(st0, r);
+            pdl_wait();
+        } else {
+            pdl_wait();
+            pdl_trigger();
+            load_stage(st0, r);
+        }
         while (r < nrounds) {
             load_stage(st1, r + step);
             compute_stage(st0, r);
@@ -510,6 +524,8 @@ template <typename Elem>
 __global__ void gather_cols_kernel(const Elem* __restrict__ src, int64_t M, int64_t ld_src,
                                    const int64_t* __restrict__ cols, int64_t ncols, int64_t ncols_padded,
                                    Elem* __restrict__ dst, int64_t ld_dst) {
+    pdl_wait();  // src may come from the kernel ahead
+    pdl_trigger();
     const int64_t total = M * ncols_padded;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / ncols_padded, j = i - m * ncols_padded;
@@ -529,16 +545,16 @@ cudaError_t stream_pick_mt(StreamParams p, cudaStream_t s) {
         const int64_t left = p.M - m0;
         p.m0 = m0;
         if (left > 32) {
-            w8a16_stream_kernel<A, VEC, 8><<<grid, kWarps * 32, 0, s>>>(p);
+            launch_dependent(w8a16_stream_kernel<A, VEC, 8>, grid, kWarps * 32, 0, s, p);
             m0 += 64;
         } else if (left > 16) {
-            w8a16_stream_kernel<A, VEC, 4><<<grid, kWarps * 32, 0, s>>>(p);
+            launch_dependent(w8a16_stream_kernel<A, VEC, 4>, grid, kWarps * 32, 0, s, p);
             m0 += 32;
         } else if (left > 8) {
-            w8a16_stream_kernel<A, VEC, 2><<<grid, kWarps * 32, 0, s>>>(p);
+            launch_dependent(w8a16_stream_kernel<A, VEC, 2>, grid, kWarps * 32, 0, s, p);
             m0 += 16;
         } else {
-            w8a16_stream_kernel<A, VEC, 1><<<grid, kWarps * 32, 0, s>>>(p);
+            launch_dependent(w8a16_stream_kernel<A, VEC, 1>, grid, kWarps * 32, 0, s, p);
             m0 += 8;
         }
     }
@@ -556,10 +572,10 @@ cudaError_t stream_fast(StreamParams p, cudaStream_t s) {
         const int64_t left = p.M - m0;
         p.m0 = m0;
         if (left > 8) {
-            w8a16_stream_fast_kernel<A, 2><<<grid, kWarps * 32, 0, s>>>(p);
+            launch_dependent(w8a16_stream_fast_kernel<A, 2>, grid, kWarps * 32, 0, s, p);
             m0 += 16;
         } else {
-            w8a16_stream_fast_kernel<A, 1><<<grid, kWarps * 32, 0, s>>>(p);
+            launch_dependent(w8a16_stream_fast_kernel<A, 1>, grid, kWarps * 32, 0, s, p);
             m0 += 8;
         }
     }
@@ -586,7 +602,7 @@ cudaError_t launch_w8a16_stream(const W8A16Args& a, cudaStream_t s) {
     p.scales = a.scales; p.scales_dtype = a.scales_dtype;
     p.bias = a.bias; p.bias_dtype = a.bias_dtype;
     p.xo = a.xo; p.wo = a.wo; p.KO = a.KO; p.ldxo = a.ldxo;
-    p.y = a.y; p.ldy = a.ldy; p.m0 = 0;
+    p.y = a.y; p.ldy = a.ldy; p.m0 = 0; p.weights_ready = a.weights_ready ? 1 : 0;
     if (a.act_dtype == kBF16) return stream_pick_vec<__nv_bfloat16>(p, s);
     if (a.act_dtype == kF16) return stream_pick_vec<__half>(p, s);
     return cudaErrorInvalidValue;
@@ -599,11 +615,11 @@ cudaError_t launch_gather_cols(const void* src, int64_t M, int64_t ld_src, const
     if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
     if (blocks < 1) blocks = 1;
     if (elem_size == 2)
-        gather_cols_kernel<uint16_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), M, ld_src,
+        launch_dependent(gather_cols_kernel<uint16_t>, (unsigned)blocks, 256, 0, s, static_cast<const uint16_t*>(src), M, ld_src,
                                                                         cols, ncols, ncols_padded, static_cast<uint16_t*>(dst),
                                                                         ld_dst);
     else
-        gather_cols_kernel<uint32_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint32_t*>(src), M, ld_src,
+        launch_dependent(gather_cols_kernel<uint32_t>, (unsigned)blocks, 256, 0, s, static_cast<const uint32_t*>(src), M, ld_src,
                                                                         cols, ncols, ncols_padded, static_cast<uint32_t*>(dst),
                                                                         ld_dst);
     return cudaPeekAtLastError();

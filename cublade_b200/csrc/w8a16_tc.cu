@@ -138,6 +138,8 @@ struct TcParams {
     const void* xo;  // [M, KO] 16-bit
     const void* wo;  // [N, KO] 16-bit
     int64_t KO, ldxo;
+    int weights_ready;  // 1: the int8 weights were not written by the kernel ahead in the stream (see W8A16Args)
+    int side_vec;    // 1: KO % 8 == 0, ldxo % 8 == 0, xo and wo 16-byte aligned -> the side product reads 16-byte chunks
     void* y;
     int64_t ldy;
     int tile_x;      // activation rows per tile (multiple of 16, <= 256)
@@ -179,6 +181,26 @@ __device__ __forceinline__ bool work_item(const TcParams& p, int num_kb, int idx
 constexpr int kMaxKO = 512;
 
 
+// side += sum over the eight 16-bit pairs of two 16-byte chunks (activation chunk x, weight chunk w), in order
+template <typename A>
+__device__ __forceinline__ float dot8(const uint4& x, const uint4& w, float side) {
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float2 a, b;
+        if constexpr (Widen<A>::kBf16) {
+            a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[k]));
+            b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[k]));
+        } else {
+            a = __half22float2(*reinterpret_cast<const __half2*>(&xw[k]));
+            b = __half22float2(*reinterpret_cast<const __half2*>(&ww[k]));
+        }
+        side = fmaf(a.x, b.x, side);
+        side = fmaf(a.y, b.y, side);
+    }
+    return side;
+}
+
 // Epilogue of one K-split of a tile (one warp = 32 output features x tile_x rows): store the fp32
 // partial accumulator to this split's slab, [row][feature] so that a warp writes 128 contiguous
 // bytes per row.  Kept out of line: the code of the ordinary epilogue is not affected by it.
@@ -209,6 +231,8 @@ __device__ __noinline__ void epilogue_split(const TcParams& p, uint32_t taddr, u
 // the slabs in split order and finishes the row (scale, outlier side product, bias, one rounding).
 template <typename A>
 __global__ void __launch_bounds__(256) w8a16_tc_fixup_kernel(const __grid_constant__ TcParams p, int grid_main) {
+    pdl_wait();  // the slabs come from the kernel ahead
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blocks_per_tile = (p.tile_x + 7) / 8;
     const int j = blockIdx.x / blocks_per_tile;                      // tile of the split round
@@ -284,6 +308,11 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic launch edge.  This CTA may be running while the kernel ahead of it in the stream has not finished:
+    // barriers, tensor memory and the weight stream (weights_ready) are set up under that kernel's tail, and every warp
+    // that touches what that kernel may have written -- the activation producer, the epilogue (outlier activations,
+    // the output, the K-split slabs) -- waits for it first.  The kernel behind this one may be set up in turn.
+    if (p.weights_ready) pdl_trigger();
 
     // Tensor-memory modes: widen the k-blocks of work item w that belong to converter group `group` (every
     // kConvGroups-th k-block of the CTA's running count) into their tensor-memory stages.  A thread owns weight row
@@ -342,6 +371,8 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // phase is complete and issuing a TMA ~100, so one thread feeding both rings cannot stay
         // ahead of the tensor core.
         if (lane == 0) {
+            pdl_wait();
+            if (!p.weights_ready) pdl_trigger();
             uint32_t s = 0, ph = 0;
             bool ok = true;
             WorkItem w;
@@ -361,6 +392,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     } else if (warp == kW8Warp) {
         // ------------------------------ TMA producer, int8 weights ------------------------------
         if (lane == 0) {
+            if (!p.weights_ready) pdl_wait();
             constexpr int kAhead = 12;  // k-blocks of weights requested into L2 ahead of their TMA load
             uint32_t s = 0, ph = 0;
             bool ok = true;
@@ -452,6 +484,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // ------------------------------ epilogue ------------------------------
         const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
         const A* xo = static_cast<const A*>(p.xo);
+        pdl_wait();
         const A* wo = static_cast<const A*>(p.wo);
         A* y = static_cast<A*>(p.y);
         uint32_t it = 0;
@@ -472,6 +505,14 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const float scale = n_ok ? ref_round<A>(load_scalar(p.scales, p.scales_dtype, n)) : 0.0f;
             const bool has_bias = p.bias != nullptr;
             const float bias = (n_ok && has_bias) ? ref_round<A>(load_scalar(p.bias, p.bias_dtype, n)) : 0.0f;
+            // this lane's outlier weights, 16 bytes = eight columns per chunk (see side_vec)
+            constexpr int kSideRegs = 4;
+            const int side_chunks = p.side_vec ? (int)(p.KO >> 3) : 0;
+            const uint4* wrow4 = reinterpret_cast<const uint4*>(wo + (n_ok ? n : 0) * p.KO);
+            uint4 wreg[kSideRegs];
+#pragma unroll
+            for (int ch = 0; ch < kSideRegs; ++ch)
+                wreg[ch] = (n_ok && ch < side_chunks) ? __ldg(wrow4 + ch) : make_uint4(0u, 0u, 0u, 0u);
             {
                 int okw = 1;
                 if (lane == 0) {
@@ -518,10 +559,21 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         // side product over the outlier columns: the activation row is the same address
                         // in every lane (broadcast load), the weight row is this lane's own
                         const A* xrow = xo + m * p.ldxo;
-                        const A* wrow = wo + n * p.KO;
                         float side = 0.0f;
-                        for (int j = 0; j < (int)p.KO; ++j)
-                            side = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), side);
+                        if (p.side_vec) {
+                            // 16-byte chunks of eight columns; this lane's first kSideRegs weight chunks were
+                            // fetched once per tile, an activation chunk costs one broadcast load per row
+                            const uint4* xr = reinterpret_cast<const uint4*>(xrow);
+#pragma unroll
+                            for (int ch = 0; ch < kSideRegs; ++ch)
+                                if (ch < side_chunks) side = dot8<A>(__ldg(xr + ch), wreg[ch], side);
+                            for (int ch = kSideRegs; ch < side_chunks; ++ch)
+                                side = dot8<A>(__ldg(xr + ch), __ldg(wrow4 + ch), side);
+                        } else {
+                            const A* wrow = wo + n * p.KO;
+                            for (int j = 0; j < (int)p.KO; ++j)
+                                side = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), side);
+                        }
                         v = ref_round<A>(v + ref_round<A>(side));
                     }
                     if (has_bias) v = ref_round<A>(v + bias);
@@ -770,8 +822,7 @@ static cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& m
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    w8a16_tc_kernel<A, MODE><<<grid, kThreads, C::kSmemBytes, s>>>(map_x, map_w, map_pf, p);
-    return cudaPeekAtLastError();
+    return launch_dependent(w8a16_tc_kernel<A, MODE>, grid, kThreads, C::kSmemBytes, s, map_x, map_w, map_pf, p);
 }
 
 cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
@@ -781,6 +832,9 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     p.scales = a.scales; p.scales_dtype = a.scales_dtype;
     p.bias = a.bias; p.bias_dtype = a.bias_dtype;
     p.xo = a.xo; p.wo = a.wo; p.KO = a.KO; p.ldxo = a.ldxo;
+    p.weights_ready = a.weights_ready ? 1 : 0;
+    p.side_vec = a.KO > 0 && a.KO % 8 == 0 && a.ldxo % 8 == 0 && (reinterpret_cast<uintptr_t>(a.xo) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(a.wo) & 15) == 0;
     p.y = a.y; p.ldy = a.ldy;
     TcPlan pl = make_plan(a.M, a.N, a.K, sms, true);
     const bool ws_ok = a.workspace && a.workspace_bytes >= pl.workspace_bytes() &&
@@ -822,10 +876,9 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
                   : launch_variant<__half, kTmemA64>(map_x, map_w, map_pf, p, grid, s);
     if (e != cudaSuccess || pl.splits <= 1) return e;
     const unsigned fix_grid = (unsigned)(pl.rem_tiles * ((pl.tile_x + 7) / 8));
-    if (bf16) w8a16_tc_fixup_kernel<__nv_bfloat16><<<fix_grid, 256, 0, s>>>(p, pl.grid);
-    else w8a16_tc_fixup_kernel<__half><<<fix_grid, 256, 0, s>>>(p, pl.grid);
     count_launches(1);  // the fix-up kernel, beyond the one launch the C entry point accounts for
-    return cudaPeekAtLastError();
+    if (bf16) return launch_dependent(w8a16_tc_fixup_kernel<__nv_bfloat16>, fix_grid, 256, 0, s, p, pl.grid);
+    return launch_dependent(w8a16_tc_fixup_kernel<__half>, fix_grid, 256, 0, s, p, pl.grid);
 }
 
 // 0 = no kernel of this library has hit a bounded-wait expiry on the current device

@@ -76,21 +76,59 @@ class cuBladeW8A16LinearLayer(nn.Module):
         self._dev_cache[key] = (src, src._version, moved)
         return moved
 
+    def _cached(self, key, sources, build):
+        """Derived device tensor ``key``, rebuilt when one of the ``sources`` buffers was replaced or written."""
+        stamp = tuple((id(t), t._version) for t in sources)
+        hit = self._dev_cache.get(key)
+        if hit is not None and hit[0] == stamp and all(a is b for a, b in zip(hit[1], sources)):
+            return hit[2]
+        made = build()
+        self._dev_cache[key] = (stamp, tuple(sources), made)
+        return made
+
     def _padded_weights(self, dev: torch.device, width: int) -> torch.Tensor:
-        """``int8_weights`` on ``dev`` with zero columns appended up to ``width`` (cached like ``_on``).
+        """``int8_weights`` on ``dev`` with zero columns appended up to ``width``.
 
         The tensor-core kernels fetch the int8 rows with TMA, whose row stride must be a multiple of 16
-        bytes; ``in_features - n_outliers`` seldom is.  ``state_dict()`` keeps the reference's
-        ``[out, in - n_outliers]`` shape -- the padded copy lives only in this cache."""
+        bytes.  ``state_dict()`` keeps the stored shape -- the padded copy lives only in this cache."""
         src = self.int8_weights
-        key = ("int8_weights_padded", dev, width)
-        hit = self._dev_cache.get(key)
-        if hit is not None and hit[0] is src and hit[1] == src._version:
-            return hit[2]
-        padded = torch.zeros((src.shape[0], width), dtype=torch.int8, device=dev)
-        padded[:, : src.shape[1]].copy_(src)
-        self._dev_cache[key] = (src, src._version, padded)
-        return padded
+
+        def build():
+            padded = torch.zeros((src.shape[0], width), dtype=torch.int8, device=dev)
+            padded[:, : src.shape[1]].copy_(src)
+            return padded
+
+        return self._cached(("int8_weights_padded", dev, width), (src,), build)
+
+    def _full_k_weights(self, dev: torch.device) -> torch.Tensor:
+        """The int8 codes spread back over all ``in_features`` columns, the outlier columns zero.
+
+        With it the GEMM runs on the activations as they are: a zero code adds nothing to the fp32 sum, so
+        ``x @ full.T`` equals ``x[:, normal_cols] @ int8_weights.T`` exactly, and the ``[M, in - n_outliers]``
+        re-packing of the activations (a pass over all of x per call) is not needed -- only the few outlier
+        columns are gathered.  Rows are ``in_features`` bytes, normally a multiple of 16 where
+        ``in_features - n_outliers`` is not.  ``state_dict()`` keeps the reference's compact
+        ``[out, in - n_outliers]`` buffer; this copy lives only in the cache."""
+        src, cols = self.int8_weights, self.normal_cols
+
+        def build():
+            full = torch.zeros((src.shape[0], self.in_features), dtype=torch.int8, device=dev)
+            full.index_copy_(1, cols.to(dev), src.to(dev))
+            return full
+
+        return self._cached(("int8_weights_full_k", dev), (src, cols), build)
+
+    def _padded_outlier_weights(self, dev: torch.device, dtype: torch.dtype, width: int) -> torch.Tensor:
+        """``outlier_weights`` in the activation dtype with zero columns up to ``width`` (a multiple of 8, so that
+        rows are whole 16-byte chunks for the side product)."""
+        src = self.outlier_weights
+
+        def build():
+            padded = torch.zeros((src.shape[0], width), dtype=dtype, device=dev)
+            padded[:, : src.shape[1]].copy_(src)
+            return padded
+
+        return self._cached(("outlier_weights_padded", dev, dtype, width), (src,), build)
 
     def forward(self, x: torch.Tensor):
         """``y = x @ dequant(W).T (+ outlier columns in 16-bit) (+ bias)`` on the GPU, shape ``[..., out]``.
@@ -108,7 +146,6 @@ class cuBladeW8A16LinearLayer(nn.Module):
         if x2d.stride(-1) != 1:
             x2d = x2d.contiguous()
         dev = x2d.device
-        wq = self._on("int8_weights", dev)
         scales = self._on("scales", dev)
         bias = None
         if self.bias is not None:
@@ -118,18 +155,11 @@ class cuBladeW8A16LinearLayer(nn.Module):
             bias = bias.contiguous()
 
         if self.handle_outliers and self.outlier_cols is not None and len(self.outlier_cols) > 0:
-            normal_idx = self._on("normal_cols", dev)
             outlier_idx = self._on("outlier_cols", dev)
-            w_out = self._on("outlier_weights", dev, x2d.dtype)
-            kn = wq.shape[1]
-            if kn % 16 and x2d.shape[0] > 16:  # the tensor-core kernels need 16-byte int8 rows: pad K with zeros
-                width = (kn + 15) // 16 * 16
-                wq = self._padded_weights(dev, width)
-                x_normal = gather_columns(x2d, normal_idx, pad_to=width)
-            else:
-                x_normal = gather_columns(x2d, normal_idx)
-            x_out = gather_columns(x2d, outlier_idx)
-            y2d = w8a16_linear(x_normal, wq, scales, bias, x_out, w_out)
+            ko = (len(self.outlier_cols) + 7) // 8 * 8
+            x_out = gather_columns(x2d, outlier_idx, pad_to=ko)
+            y2d = w8a16_linear(x2d, self._full_k_weights(dev), scales, bias, x_out,
+                               self._padded_outlier_weights(dev, x2d.dtype, ko))
         elif self.in_features % 16 and x2d.shape[0] > 16:
             width = (self.in_features + 15) // 16 * 16
             every = self._dev_cache.get(("arange", dev))
@@ -137,7 +167,7 @@ class cuBladeW8A16LinearLayer(nn.Module):
                 every = self._dev_cache[("arange", dev)] = torch.arange(self.in_features, device=dev)
             y2d = w8a16_linear(gather_columns(x2d, every, pad_to=width), self._padded_weights(dev, width), scales, bias)
         else:
-            y2d = w8a16_linear(x2d, wq, scales, bias)
+            y2d = w8a16_linear(x2d, self._on("int8_weights", dev), scales, bias)
         return y2d.view(*lead, self.out_features)
 
 

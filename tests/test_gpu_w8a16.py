@@ -274,7 +274,7 @@ def ref_variant(request):
 @pytest.mark.parametrize("M", [1, 16, 128, 2048])
 def test_forward_against_the_reference_layers_recorded_outputs(ref_gold, ref_variant, M):
     """Benchmark shape (N = 14336, K = 4096; K - 8 = 4088 int8 columns in the LLM.int8 variant, which the layer
-    pads to 4096 for the tensor-core kernels).  Gate: the stated tolerance; and because the epilogue rounds in
+    spreads back over 4096 columns, the outlier columns zero, for the GEMM).  Gate: the stated tolerance; and because the epilogue rounds in
     the reference's places, fewer than 0.5 % of the bf16 values may differ at all (accumulation order)."""
     import hashlib
 
@@ -297,9 +297,11 @@ def test_forward_against_the_reference_layers_recorded_outputs(ref_gold, ref_var
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K,n_out", [(200, 512, 1040, 8), (300, 640, 4096, 8), (200, 256, 520, 0)])
 def test_int8_rows_that_are_not_16_byte_multiples_take_the_tensor_core_path(M, N, K, n_out, dtype):
-    """in_features - n_outliers (or in_features itself) = 8 mod 16: the layer pads K with zero columns in a cached
-    copy of the int8 weights and in the re-packed activations, so the tensor-core kernel serves the call (one
-    launch after the gathers, not a chain of streaming launches); the state dict keeps the unpadded shape."""
+    """in_features - n_outliers (or in_features itself) = 8 mod 16, which the tensor-core kernel's TMA loads cannot
+    address.  With outliers the layer runs the GEMM over all in_features columns of a cached copy of the int8 weights
+    whose outlier columns are zero (only the few outlier activations are gathered); without, it pads K with zero columns
+    in a cached copy of the weights and in the re-packed activations.  Either way the tensor-core kernel serves the
+    call (one launch after the gather, not a chain of streaming launches); the state dict keeps the stored shape."""
     import cublade_b200 as cb
     from cublade_b200 import _native as Nat
 

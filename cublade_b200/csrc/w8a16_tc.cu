@@ -505,9 +505,14 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const float scale = n_ok ? ref_round<A>(load_scalar(p.scales, p.scales_dtype, n)) : 0.0f;
             const bool has_bias = p.bias != nullptr;
             const float bias = (n_ok && has_bias) ? ref_round<A>(load_scalar(p.bias, p.bias_dtype, n)) : 0.0f;
-            // this lane's outlier weights, 16 bytes = eight columns per chunk (see side_vec)
-            constexpr int kSideRegs = 4;
+            // Outlier side product (see side_vec): 16-byte chunks of eight columns.  Up to kSideRegs chunks (16 outlier
+            // columns) stay in registers: this lane's weight chunks are fetched once per tile, and the activation chunks
+            // of a 32-row block are fetched by ONE load per chunk -- lane l takes row l -- right after the block's
+            // tensor-memory load is issued, then handed round the warp by shuffles.  A global load per output row, even
+            // eight at a time, left the epilogue longer than the tile's main loop (M = 2048: 371 against 240 us).
+            constexpr int kSideRegs = 2;
             const int side_chunks = p.side_vec ? (int)(p.KO >> 3) : 0;
+            const bool side_fast = side_chunks > 0 && side_chunks <= kSideRegs;
             const uint4* wrow4 = reinterpret_cast<const uint4*>(wo + (n_ok ? n : 0) * p.KO);
             uint4 wreg[kSideRegs];
 #pragma unroll
@@ -549,35 +554,83 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(r2[c]));
                     }
                 }
+                // this block's outlier activations: row c0 + lane, one 16-byte chunk per register (rows beyond M re-read
+                // row M - 1); issued before the wait so that the loads fly with the tensor-memory load
+                uint4 xblk[kSideRegs];
+                if (side_fast) {
+                    const int64_t mr = m_base + c0 + lane;
+                    const uint4* xr = reinterpret_cast<const uint4*>(xo + (mr < p.M ? mr : p.M - 1) * p.ldxo);
+#pragma unroll
+                    for (int ch = 0; ch < kSideRegs; ++ch)
+                        xblk[ch] = ch < side_chunks ? __ldg(xr + ch) : make_uint4(0u, 0u, 0u, 0u);
+                }
                 tmem_ld_wait();
+                if (side_fast || p.KO == 0) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int64_t m = m_base + c0 + c;
-                    if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
-                    float v = ref_round<A>(ref_round<A>(__uint_as_float(r[c])) * scale);
-                    if (p.KO > 0 && n_ok) {
-                        // side product over the outlier columns: the activation row is the same address
-                        // in every lane (broadcast load), the weight row is this lane's own
-                        const A* xrow = xo + m * p.ldxo;
-                        float side = 0.0f;
-                        if (p.side_vec) {
-                            // 16-byte chunks of eight columns; this lane's first kSideRegs weight chunks were
-                            // fetched once per tile, an activation chunk costs one broadcast load per row
-                            const uint4* xr = reinterpret_cast<const uint4*>(xrow);
+                    for (int c = 0; c < 32; ++c) {
+                        const int64_t m = m_base + c0 + c;
+                        if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
+                        float v = ref_round<A>(ref_round<A>(__uint_as_float(r[c])) * scale);
+                        if (side_fast) {
+                            float side = 0.0f;
 #pragma unroll
-                            for (int ch = 0; ch < kSideRegs; ++ch)
-                                if (ch < side_chunks) side = dot8<A>(__ldg(xr + ch), wreg[ch], side);
-                            for (int ch = kSideRegs; ch < side_chunks; ++ch)
-                                side = dot8<A>(__ldg(xr + ch), __ldg(wrow4 + ch), side);
-                        } else {
-                            const A* wrow = wo + n * p.KO;
-                            for (int j = 0; j < (int)p.KO; ++j)
-                                side = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), side);
+                            for (int ch = 0; ch < kSideRegs; ++ch) {
+                                if (ch < side_chunks) {
+                                    uint4 xv;
+                                    xv.x = __shfl_sync(0xffffffffu, xblk[ch].x, c);
+                                    xv.y = __shfl_sync(0xffffffffu, xblk[ch].y, c);
+                                    xv.z = __shfl_sync(0xffffffffu, xblk[ch].z, c);
+                                    xv.w = __shfl_sync(0xffffffffu, xblk[ch].w, c);
+                                    side = dot8<A>(xv, wreg[ch], side);
+                                }
+                            }
+                            v = ref_round<A>(v + ref_round<A>(side));
                         }
-                        v = ref_round<A>(v + ref_round<A>(side));
+                        if (has_bias) v = ref_round<A>(v + bias);
+                        if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
                     }
-                    if (has_bias) v = ref_round<A>(v + bias);
-                    if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
+                    continue;
+                }
+                // more outlier columns than the registers hold, or unaligned operands: loads in the loop, eight output
+                // rows at a time so that eight of them are in flight
+#pragma unroll
+                for (int cb = 0; cb < 32; cb += 8) {
+                    if (m_base + c0 + cb >= p.M || c0 + cb >= p.tile_x) break;  // uniform across the warp
+                    float side[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) side[u] = 0.0f;
+                    if (p.side_vec) {
+                        for (int ch = 0; ch < side_chunks; ++ch) {
+                            const uint4 wv = n_ok ? __ldg(wrow4 + ch) : make_uint4(0u, 0u, 0u, 0u);
+                            uint4 xv[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int64_t mr = m_base + c0 + cb + u;
+                                xv[u] = __ldg(reinterpret_cast<const uint4*>(xo + (mr < p.M ? mr : p.M - 1) * p.ldxo) + ch);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) side[u] = dot8<A>(xv[u], wv, side[u]);
+                        }
+                    } else if (n_ok) {
+                        const A* wrow = wo + n * p.KO;
+                        for (int j = 0; j < (int)p.KO; ++j) {
+                            const float wj = Widen<A>::to_float(__ldg(wrow + j));
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int64_t mr = m_base + c0 + cb + u;
+                                side[u] = fmaf(Widen<A>::to_float(__ldg(xo + (mr < p.M ? mr : p.M - 1) * p.ldxo + j)), wj, side[u]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int64_t m = m_base + c0 + cb + u;
+                        if (m >= p.M || c0 + cb + u >= p.tile_x) break;  // uniform across the warp
+                        float v = ref_round<A>(ref_round<A>(__uint_as_float(r[cb + u])) * scale);
+                        v = ref_round<A>(v + ref_round<A>(side[u]));
+                        if (has_bias) v = ref_round<A>(v + bias);
+                        if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
+                    }
                 }
             }
             tc_fence_before();

@@ -218,6 +218,22 @@ struct Widen<__nv_bfloat16> {
     }
     __device__ __forceinline__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+    // Packed pairs (low half = first value).  pack2 rounds two floats to the type; mul2 / add2 round the exact product /
+    // sum of the pairs once -- the same value as rounding the float32 product / sum, which is exact or off by far less
+    // than half a unit of the 16-bit type whenever float32 has to round it.  The _rn forms are never contracted into
+    // a fused multiply-add, which would drop the rounding between the two steps.
+    __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    __device__ __forceinline__ static uint32_t mul2(uint32_t a, uint32_t b) {
+        const __nv_bfloat162 v = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    __device__ __forceinline__ static uint32_t add2(uint32_t a, uint32_t b) {
+        const __nv_bfloat162 v = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
 };
 template <>
 struct Widen<__half> {
@@ -234,6 +250,18 @@ struct Widen<__half> {
     }
     __device__ __forceinline__ static float to_float(__half v) { return __half2float(v); }
     __device__ __forceinline__ static __half from_float(float v) { return __float2half_rn(v); }
+    __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+        const __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    __device__ __forceinline__ static uint32_t mul2(uint32_t a, uint32_t b) {
+        const __half2 v = __hmul2_rn(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    __device__ __forceinline__ static uint32_t add2(uint32_t a, uint32_t b) {
+        const __half2 v = __hadd2_rn(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
 };
 
 // v rounded to the activation type A and widened back.  The reference's forward materialises a

@@ -48,6 +48,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 namespace cb {
 
@@ -505,6 +506,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const float scale = n_ok ? ref_round<A>(load_scalar(p.scales, p.scales_dtype, n)) : 0.0f;
             const bool has_bias = p.bias != nullptr;
             const float bias = (n_ok && has_bias) ? ref_round<A>(load_scalar(p.bias, p.bias_dtype, n)) : 0.0f;
+            const uint32_t scale2 = Widen<A>::pack2(scale, scale), bias2 = Widen<A>::pack2(bias, bias);
             // Outlier side product (see side_vec): 16-byte chunks of eight columns.  Up to kSideRegs chunks (16 outlier
             // columns) stay in registers: this lane's weight chunks are fetched once per tile, and the activation chunks
             // of a 32-row block are fetched by ONE load per chunk -- lane l takes row l -- right after the block's
@@ -565,30 +567,60 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         xblk[ch] = ch < side_chunks ? __ldg(xr + ch) : make_uint4(0u, 0u, 0u, 0u);
                 }
                 tmem_ld_wait();
-                if (side_fast || p.KO == 0) {
+                // Rows of this block that exist; the per-row work below is free of control flow (stores are predicated,
+                // flags are selects) so that the compiler interleaves the 32 independent rows -- with an early exit per
+                // row every row was a basic block of its own and its chain of dependent conversions ran unhidden
+                // (measured: a bias cost 6 % of the whole kernel, eight outlier columns 80 %).
+                const int64_t rows_left = p.M - (m_base + c0);
+                const int nrows = (int)(rows_left < 32 ? rows_left : 32) < p.tile_x - c0 ? (int)(rows_left < 32 ? rows_left : 32)
+                                                                                       : p.tile_x - c0;
+                // Two rows at a time in packed 16-bit arithmetic: one conversion rounds both accumulators, one packed
+                // multiply applies the scale, one packed add each the outlier product and the bias -- every step rounded
+                // to the activation type like the reference's chain of kernels -- then two 16-bit stores.  The epilogue
+                // warps share the SM's issue slots with the converter warps, which pace the main loop: an instruction
+                // saved per output row here is time given back to the next tile's main loop.
+                uint16_t* yrow = reinterpret_cast<uint16_t*>(y + (m_base + c0) * p.ldy + n);
+                const int64_t ystep = p.ldy;
+                if (p.KO == 0) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int64_t m = m_base + c0 + c;
-                        if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
-                        float v = ref_round<A>(ref_round<A>(__uint_as_float(r[c])) * scale);
-                        if (side_fast) {
-                            float side = 0.0f;
+                    for (int c = 0; c < 32; c += 2) {
+                        uint32_t v = Widen<A>::mul2(Widen<A>::pack2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2);
+                        v = has_bias ? Widen<A>::add2(v, bias2) : v;
+                        if (n_ok && c < nrows) yrow[(int64_t)c * ystep] = (uint16_t)(v & 0xffffu);
+                        if (n_ok && c + 1 < nrows) yrow[(int64_t)(c + 1) * ystep] = (uint16_t)(v >> 16);
+                    }
+                    continue;
+                }
+                if (side_fast) {
+                    auto rows32 = [&](auto two_chunks) {
 #pragma unroll
-                            for (int ch = 0; ch < kSideRegs; ++ch) {
-                                if (ch < side_chunks) {
-                                    uint4 xv;
-                                    xv.x = __shfl_sync(0xffffffffu, xblk[ch].x, c);
-                                    xv.y = __shfl_sync(0xffffffffu, xblk[ch].y, c);
-                                    xv.z = __shfl_sync(0xffffffffu, xblk[ch].z, c);
-                                    xv.w = __shfl_sync(0xffffffffu, xblk[ch].w, c);
-                                    side = dot8<A>(xv, wreg[ch], side);
+                        for (int c = 0; c < 32; c += 2) {
+                            float side[2];
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                uint4 xv;
+                                xv.x = __shfl_sync(0xffffffffu, xblk[0].x, c + u);
+                                xv.y = __shfl_sync(0xffffffffu, xblk[0].y, c + u);
+                                xv.z = __shfl_sync(0xffffffffu, xblk[0].z, c + u);
+                                xv.w = __shfl_sync(0xffffffffu, xblk[0].w, c + u);
+                                side[u] = dot8<A>(xv, wreg[0], 0.0f);
+                                if constexpr (decltype(two_chunks)::value) {
+                                    xv.x = __shfl_sync(0xffffffffu, xblk[1].x, c + u);
+                                    xv.y = __shfl_sync(0xffffffffu, xblk[1].y, c + u);
+                                    xv.z = __shfl_sync(0xffffffffu, xblk[1].z, c + u);
+                                    xv.w = __shfl_sync(0xffffffffu, xblk[1].w, c + u);
+                                    side[u] = dot8<A>(xv, wreg[1], side[u]);
                                 }
                             }
-                            v = ref_round<A>(v + ref_round<A>(side));
+                            uint32_t v = Widen<A>::mul2(Widen<A>::pack2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2);
+                            v = Widen<A>::add2(v, Widen<A>::pack2(side[0], side[1]));
+                            v = has_bias ? Widen<A>::add2(v, bias2) : v;
+                            if (n_ok && c < nrows) yrow[(int64_t)c * ystep] = (uint16_t)(v & 0xffffu);
+                            if (n_ok && c + 1 < nrows) yrow[(int64_t)(c + 1) * ystep] = (uint16_t)(v >> 16);
                         }
-                        if (has_bias) v = ref_round<A>(v + bias);
-                        if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
-                    }
+                    };
+                    if (side_chunks > 1) rows32(std::true_type{});
+                    else rows32(std::false_type{});
                     continue;
                 }
                 // more outlier columns than the registers hold, or unaligned operands: loads in the loop, eight output

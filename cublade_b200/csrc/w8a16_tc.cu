@@ -80,16 +80,26 @@ constexpr uint32_t kBytesW8 = kTileN * kBlockK;  // 8192
 //           A stages, so the operand ring is eight k-blocks deep -- with one tile per CTA (M <= 128) the kernel is
 //           a weight stream whose pace is set by how many k-blocks are in flight, not by the tensor core.
 //   kTmemA64: the same for tiles of at most 64 rows: twelve stages.
-enum AMode : int { kSmemA = 0, kTmemA = 1, kTmemA128 = 2, kTmemA64 = 3 };
+//   kTmemA2: kTmemA with TWO activation tiles of up to 208 rows per work item: a widened weight k-block in tensor
+//           memory is used by two MMAs, one per activation tile, each into its own accumulator.  What bounds the
+//           one-tile modes at large M is shared-memory bandwidth -- per k-block the activation tile is written once
+//           by TMA and read once by the tensor core, the int8 tile written and read once: 112 KiB (kSmemA, 256
+//           rows) or 80 KiB (kTmemA, 208 rows) against 128 B/clk -- and the converters' issue slots; both costs are
+//           per weight k-block, so a second activation tile halves them per output row (120 KiB for 416 rows).
+//           The two accumulators fill tensor memory beside three A stages, so they are not double-buffered: the
+//           next work item's MMAs into an accumulator wait until the epilogue has drained it (a few microseconds
+//           per ~30 us item).
+enum AMode : int { kSmemA = 0, kTmemA = 1, kTmemA128 = 2, kTmemA64 = 3, kTmemA2 = 4 };
 
 template <int MODE>
 struct Cfg {
-    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : (MODE == kTmemA ? 208 : (MODE == kTmemA128 ? 128 : 64));  // activation rows per tile = UMMA N
+    static constexpr int kMaxTileX = MODE == kSmemA ? 256 : (MODE == kTmemA || MODE == kTmemA2 ? 208 : (MODE == kTmemA128 ? 128 : 64));  // activation rows per tile = UMMA N
+    static constexpr int kHalves = MODE == kTmemA2 ? 2 : 1;  // activation tiles (and accumulators) per work item
     // ONE operand ring: stage s holds the activation tile and the widened weight tile of a k-block, one
     // "full" barrier (TMA bytes + the eight converter warps) and one "empty" barrier (one tcgen05.commit) per
     // stage -- the MMA thread's loop is the critical path of the kernel, and every barrier it probes or
     // commits to costs it time the tensor core spends idle.
-    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 6 : (MODE == kTmemA128 ? 8 : 12));
+    static constexpr int kStages = MODE == kSmemA ? 4 : (MODE == kTmemA ? 6 : (MODE == kTmemA128 ? 8 : (MODE == kTmemA64 ? 12 : 3)));
     // kTmemA: only three 32-column A stages fit beside two 208-column accumulators, but shared memory holds six
     // activation + int8 stages: ring slot s uses tensor-memory A stage s % 3, and a converter waits, besides the int8
     // tile, for the MMAs of the k-block three slots back (the `empty` barrier of that slot) before it overwrites the stage.
@@ -98,7 +108,7 @@ struct Cfg {
     // them, whatever their size, so with short activation tiles one issuer, not the tensor core, sets the pace.
     // Issuer i takes the k-blocks of parity i of a work item and accumulates into accumulator i; the epilogue adds
     // the two (the accumulators then do not alternate between tiles: short tiles drain in a few hundred cycles).
-    static constexpr bool kDual = MODE >= kTmemA128;
+    static constexpr bool kDual = MODE == kTmemA128 || MODE == kTmemA64;
     // ... and THREE converter groups of four warps (one warp per tensor-memory lane quarter, the whole 64 k of
     // its 32 weight rows), each taking every third k-block: a warp's chain per k-block -- barrier probe, shared-
     // memory loads, widening, tcgen05.st, wait::st, fence, arrive -- is ~600 cycles of mostly latency, and with all
@@ -113,7 +123,8 @@ struct Cfg {
     static constexpr int kAccStride = kMaxTileX;                   // columns between the two accumulators
     static constexpr int kACol = 2 * kMaxTileX;                    // first tensor-memory column of the A stages (kTmemA)
     static constexpr int kAColsPerStage = kBlockK / 2;             // two 16-bit k per 32-bit column
-    static constexpr uint32_t kBytesX = kMaxTileX * kBlockK * 2;  // 32768 / 26624, both multiples of 1024
+    static constexpr uint32_t kBytesXHalf = kMaxTileX * kBlockK * 2;  // 32768 / 26624, both multiples of 1024
+    static constexpr uint32_t kBytesX = kHalves * kBytesXHalf;
     static constexpr uint32_t kBytesA = MODE == kSmemA ? kTileN * kBlockK * 2 : 0;
     // shared memory map
     static constexpr uint32_t x = 0;
@@ -144,7 +155,7 @@ struct TcParams {
     void* y;
     int64_t ldy;
     int tile_x;      // activation rows per tile (multiple of 16, <= 256)
-    int tiles_x;     // ceil(M / tile_x)
+    int tiles_x;     // ceil(M / (tile_x * activation tiles per work item))
     int tiles_n;     // ceil(N / 128)
     unsigned int* error_flag;  // global; set to 1 when a bounded wait expired
     // schedule (see work_item)
@@ -378,14 +389,17 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             bool ok = true;
             WorkItem w;
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx) {
-                const int row_x = (w.tile % p.tiles_x) * p.tile_x;
+                const int row_x = (w.tile % p.tiles_x) * p.tile_x * C::kHalves;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     {
                         ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag);
                     }
                     if (!ok) break;
-                    mbar_expect_tx(full_x + 8 * s, x_bytes);
+                    mbar_expect_tx(full_x + 8 * s, x_bytes * C::kHalves);
                     tma_load_2d(sx + s * kBytesX, &map_x, kb * kBlockK, row_x, full_x + 8 * s);
+                    // second activation tile of the item (rows beyond M arrive as zeros)
+                    if constexpr (C::kHalves == 2)
+                        tma_load_2d(sx + s * kBytesX + C::kBytesXHalf, &map_x, kb * kBlockK, row_x + p.tile_x, full_x + 8 * s);
                     if (++s == kStagesX) { s = 0; ph ^= 1u; }
                 }
             }
@@ -436,7 +450,9 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             bool ok = true;
             WorkItem w;
             for (int idx = 0; ok && work_item(p, num_kb, idx, w); ++idx, ++it) {
-                const uint32_t acc = C::kDual ? me : (it & 1u), acc_ph = C::kDual ? (it & 1u) : ((it >> 1) & 1u);
+                // kHalves == 2: both accumulators belong to the item (one per activation tile), neither alternates
+                const uint32_t acc = C::kDual ? me : (C::kHalves == 2 ? 0u : (it & 1u));
+                const uint32_t acc_ph = (C::kDual || C::kHalves == 2) ? (it & 1u) : ((it >> 1) & 1u);
                 {
                     ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag);  // epilogue drained this accumulator
                 }
@@ -471,6 +487,19 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             umma_f16_tmem_a(d_tmem, a_tmem + (uint32_t)(8 * k), bdesc + (uint64_t)(2 * k), idesc,
                                             (kb > kb_first || k > 0) ? 1u : 0u);
                         }
+                        if constexpr (C::kHalves == 2) {
+                            // the same widened weights against the second activation tile, into the second accumulator
+                            if (kb == w.kb0) {
+                                ok = mbar_wait(tmem_empty + 8, acc_ph ^ 1u, abort_flag);
+                                if (!ok) break;
+                                tc_fence_after();
+                            }
+                            const uint64_t bdesc1 = make_kmajor_sw128_desc(sx + s_a * kBytesX + C::kBytesXHalf);
+#pragma unroll
+                            for (int k = 0; k < kBlockK / 16; ++k)
+                                umma_f16_tmem_a(d_tmem + C::kAccStride, a_tmem + (uint32_t)(8 * k), bdesc1 + (uint64_t)(2 * k), idesc,
+                                                (kb > kb_first || k > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(empty_a + 8 * s_a);  // the stage is free once these MMAs retire
                     if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
@@ -498,7 +527,8 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             const int tx = w.tile % p.tiles_x, tn = w.tile / p.tiles_x;
             // kDual: both accumulators belong to this tile (one per MMA issuer), the same barrier phase on both
-            const uint32_t acc = C::kDual ? 0u : (it & 1u), acc_ph = C::kDual ? (it & 1u) : ((it >> 1) & 1u);
+            const uint32_t acc = (C::kDual || C::kHalves == 2) ? 0u : (it & 1u);
+            const uint32_t acc_ph = (C::kDual || C::kHalves == 2) ? (it & 1u) : ((it >> 1) & 1u);
             const uint32_t second = (C::kDual && w.kb1 - w.kb0 >= 2) ? (uint32_t)C::kAccStride : 0u;  // issuer 1 had work
             const int n_local = quarter * 32 + lane;
             const int64_t n = (int64_t)tn * kTileN + n_local;
@@ -530,9 +560,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             if (!ok) break;
             tc_fence_after();
-            const int64_t m_base = (int64_t)tx * p.tile_x;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccStride;
-            if (w.split_slot >= 0) {
+            for (int half = 0; half < C::kHalves; ++half) {  // kHalves == 2: the item's two activation tiles in turn
+            const int64_t m_base = ((int64_t)tx * C::kHalves + half) * p.tile_x;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (acc + (uint32_t)half) * C::kAccStride;
+            if (C::kHalves == 1 && w.split_slot >= 0) {
                 // a K-split of a tile of the last round: rare path, kept out of line so that the code of
                 // the ordinary epilogue below is not affected by it
                 epilogue_split(p, taddr, second, w.split_slot, n_local, m_base);
@@ -544,7 +575,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
                 continue;
             }
-            for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
+            for (int c0 = 0; c0 < p.tile_x && m_base + c0 < p.M; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 if constexpr (C::kDual) {
@@ -668,9 +699,10 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(tmem_empty + 8 * acc);
+                mbar_arrive(tmem_empty + 8 * (acc + (uint32_t)half));
                 if (C::kDual) mbar_arrive(tmem_empty + 8);
             }
+            }  // half
         }
     } else if (warp < kW8Warp) {
         // ------------------------------ converters ------------------------------
@@ -825,11 +857,20 @@ struct TcPlan {
 };
 
 constexpr int kMaxSplits = 32;
+// Modelled time of a k-block of the two-tile mode relative to (rows + 512) of the one-tile shared-memory mode.
+// Measured on B200 (N = 14336, K = 4096): a k-block of a 416-row item takes 0.79 us against 0.48 us for a 256-row
+// tile -- the same time per row, both forms are bound by what an SM pulls out of L2 (~80 GB/s per SM: 61 KB and 40 KB
+// per k-block) -- so the two-tile form wins exactly where its larger items fill the rounds better:
+// M = 320 / 416 / 832 / 2048 / 4096 / 8192: 47 / 52 / 97 / 203 / 404 / 917 us against 53 / 56 / 105 / 223 / 428 / 955 us,
+// and loses at M = 256 / 512 / 1024 (45 / 82 / 132 against 41 / 72 / 115 us).
+constexpr double kTwoTileCostFactor = 1.28;
 constexpr int kSplitOverheadKb = 24;  // slab stores + the second kernel, expressed in k-blocks (measured order of magnitude)
 
 static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, int sms, bool may_split, double* cost) {
     TcPlan pl{};
-    const int64_t tiles = ((M + tx - 1) / tx) * ((N + kTileN - 1) / kTileN);
+    const int halves = mode == kTmemA2 ? 2 : 1;  // activation tiles per work item
+    const int64_t item_rows = (int64_t)tx * halves;
+    const int64_t tiles = ((M + item_rows - 1) / item_rows) * ((N + kTileN - 1) / kTileN);
     const int num_kb = (int)((K + kBlockK - 1) / kBlockK);
     pl.mode = mode;
     pl.tile_x = tx;
@@ -839,7 +880,7 @@ static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, i
     // Split only a schedule that has no full round: there the idle SMs are a plain loss.  Behind full
     // rounds the kernel is bound by what all SMs together pull out of L2, a thinly populated last round
     // runs fast, and splitting it measured no gain (M = 1024 .. 4096, N = 14336, K = 4096).
-    if (may_split && pl.full_rounds == 0 && pl.rem_tiles > 0) {
+    if (may_split && halves == 1 && pl.full_rounds == 0 && pl.rem_tiles > 0) {
         int sp = sms / pl.rem_tiles;
         if (sp > kMaxSplits) sp = kMaxSplits;
         if (sp > num_kb / 2) sp = num_kb / 2;
@@ -853,9 +894,9 @@ static TcPlan plan_for_tile(int mode, int tx, int64_t M, int64_t N, int64_t K, i
     const double tail_kb = pl.rem_tiles == 0 ? 0.0
                            : pl.splits > 1   ? (double)((num_kb + pl.splits - 1) / pl.splits + kSplitOverheadKb)
                                              : (double)num_kb;
-    // time ~ k-blocks on the busiest CTA * (tile_x + a fixed per-k-block cost expressed in rows);
+    // time ~ k-blocks on the busiest CTA * (rows of the work item + a fixed per-k-block cost expressed in rows);
     // measured: a k-block costs nearly the same for every tile height
-    *cost = ((double)pl.full_rounds * num_kb + tail_kb) * (tx + 512);
+    *cost = ((double)pl.full_rounds * num_kb + tail_kb) * (item_rows + 512);
     return pl;
 }
 
@@ -864,9 +905,10 @@ static TcPlan make_plan(int64_t M, int64_t N, int64_t K, int sms, bool may_split
     // M <= 128: one short tile per CTA, the deep-ring modes.  Above: shared-memory A (tiles up to 256 rows) against
     // tensor-memory A (up to 208 rows), whichever models shorter -- measured on B200 (N = 14336, K = 4096) the
     // tensor-memory route needs ~9 % less time per k-block and row (M = 416: 65 vs 71 us, M = 1024: 118 vs 134 us),
-    // which its smaller tiles give back when they cost an extra round (M = 4096: 446 vs 430 us).
-    int modes[2] = {kSmemA, kTmemA};
-    int n_modes = 2;
+    // which its smaller tiles give back when they cost an extra round (M = 4096: 446 vs 430 us) -- and, from two
+    // activation tiles' worth of rows, the two-tile form of the tensor-memory route (kTmemA2).
+    int modes[3] = {kSmemA, kTmemA, kTmemA2};
+    int n_modes = M > Cfg<kTmemA>::kMaxTileX ? 3 : 2;
     if (M <= Cfg<kTmemA64>::kMaxTileX) { modes[0] = kTmemA64; n_modes = 1; }
     else if (M <= Cfg<kTmemA128>::kMaxTileX) { modes[0] = kTmemA128; n_modes = 1; }
     TcPlan best{};
@@ -874,13 +916,14 @@ static TcPlan make_plan(int64_t M, int64_t N, int64_t K, int sms, bool may_split
     for (int i = 0; i < n_modes; ++i) {
         const int mode = modes[i];
         const int max_tx = mode == kSmemA ? Cfg<kSmemA>::kMaxTileX
-                           : mode == kTmemA  ? Cfg<kTmemA>::kMaxTileX
+                           : mode == kTmemA || mode == kTmemA2 ? Cfg<kTmemA>::kMaxTileX
                            : mode == kTmemA128 ? Cfg<kTmemA128>::kMaxTileX
                                                : Cfg<kTmemA64>::kMaxTileX;
         for (int tx = max_tx; tx >= 32; tx -= 16) {
             double cost;
             const TcPlan pl = plan_for_tile(mode, tx, M, N, K, sms, may_split, &cost);
             if (mode == kTmemA) cost *= 0.91;
+            if (mode == kTmemA2) cost *= kTwoTileCostFactor;
             if (cost < best_cost - 1e-9) { best_cost = cost; best = pl; }
         }
     }
@@ -928,7 +971,8 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
     p.tile_x = pl.tile_x;
     p.full_rounds = pl.full_rounds; p.rem_tiles = pl.rem_tiles; p.splits = pl.splits;
     p.partial = pl.splits > 1 ? static_cast<float*>(a.workspace) : nullptr;
-    p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
+    const int64_t item_rows = (int64_t)p.tile_x * (pl.mode == kTmemA2 ? 2 : 1);
+    p.tiles_x = (int)((a.M + item_rows - 1) / item_rows);
     p.tiles_n = (int)((a.N + kTileN - 1) / kTileN);
     p.error_flag = error_word();
     if (!p.error_flag) return cudaErrorUnknown;
@@ -955,6 +999,8 @@ cudaError_t launch_w8a16_tc(const W8A16Args& a, cudaStream_t s) {
                                     : launch_variant<__half, kSmemA>(map_x, map_w, map_pf, p, grid, s);
     else if (pl.mode == kTmemA) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA>(map_x, map_w, map_pf, p, grid, s)
                                          : launch_variant<__half, kTmemA>(map_x, map_w, map_pf, p, grid, s);
+    else if (pl.mode == kTmemA2) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA2>(map_x, map_w, map_pf, p, grid, s)
+                                          : launch_variant<__half, kTmemA2>(map_x, map_w, map_pf, p, grid, s);
     else if (pl.mode == kTmemA128) e = bf16 ? launch_variant<__nv_bfloat16, kTmemA128>(map_x, map_w, map_pf, p, grid, s)
                                             : launch_variant<__half, kTmemA128>(map_x, map_w, map_pf, p, grid, s);
     else e = bf16 ? launch_variant<__nv_bfloat16, kTmemA64>(map_x, map_w, map_pf, p, grid, s)

@@ -350,3 +350,35 @@ def test_more_than_64_outlier_columns(M):
     for path in (0, 3) if M > 16 else (0, 1):
         y = w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), None, xo.cuda(), wo.cuda(), path=path)
         _check(y, ref, f"KO=65 path {path}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K,KO,bias", [(416, 40000, 256, 0, True), (832, 19200 + 64, 448, 8, True),
+                                           (600, 19200, 320, 0, False), (417, 4096, 4096, 16, True),
+                                           (2048, 2048, 512, 0, True)])
+def test_two_activation_tiles_per_work_item(M, N, K, KO, bias, dtype):
+    """Shapes for which the planner takes the two-tile form of the tensor-memory mode (one widened weight k-block
+    multiplied with two activation tiles into two accumulators): several work items per CTA, a ragged last item whose
+    second tile is partly or wholly beyond M, ragged N, outlier columns, a bias, both activation types."""
+    from cublade_b200 import _native as Nat
+    from cublade_b200.bindings.w8a16 import w8a16_linear
+
+    g = torch.Generator().manual_seed(M + N + K + KO)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(N, generator=g).to(dtype) if bias else None
+    lay = O.w8a16_quantize(w, dtype)
+    ref = O.w8a16_forward_fp64(x, lay, b)
+    xo = wo = None
+    if KO:
+        xo = (torch.randn(M, KO, generator=g) * 4).to(dtype)
+        wo = (torch.randn(N, KO, generator=g) * 0.05).to(dtype)
+        ref = ref + xo.double() @ wo.double().T
+    y = w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda() if bias else None,
+                     xo.cuda() if KO else None, wo.cuda() if KO else None, path=3)
+    _check(y, ref, f"M={M} N={N} K={K} KO={KO}")
+    if not KO:
+        ref_order = O.w8a16_forward(x, lay, b)
+        ne = int((y.cpu().view(torch.int16) != ref_order.view(torch.int16)).sum())
+        assert ne <= 5e-3 * y.numel(), f"{ne} of {y.numel()} values differ from the reference's rounding order"
+    assert Nat.device_error_state() == 0

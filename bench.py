@@ -50,12 +50,14 @@ if str(ROOT) not in sys.path:
 L2_BYTES = 126 * 1024 * 1024
 MIN_REGION_S = 0.2  # a timed region is repeated until it lasts at least this long
 # DRAM bytes (read + write) per launch of each workload's kernels, from one ncu capture of that workload
-# (dram__bytes_read.sum + dram__bytes_write.sum); None where no capture was taken.  Stores that were still
-# dirty in the 126 MB L2 when a captured launch ended are not in its count.
+# (dram__bytes_read.sum + dram__bytes_write.sum, caches flushed before each captured launch); None where no capture
+# was taken.  Stores that were still dirty in the 126 MB L2 when a captured launch ended are not in its count.
+# "quantize" of the per-tensor workload is its two launches (amax: 33.57 MB, cast: 33.57 MB under ncu -- live, the
+# cast finds part of x in L2).
 NCU_TRAFFIC_BYTES = {
-    "int8_channel": {"quantize": 163_215_616, "dequantize": None},
-    "fp8_tensor": {"quantize": None, "dequantize": None},
-    "int8_group": {"quantize": None, "dequantize": None},
+    "int8_channel": {"quantize": 164_258_409, "dequantize": 140_661_321},
+    "fp8_tensor": {"quantize": 67_135_317, "dequantize": 16_789_163},
+    "int8_group": {"quantize": 362_416_971, "dequantize": 346_577_701},
 }
 
 

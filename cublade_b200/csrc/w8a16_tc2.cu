@@ -72,6 +72,8 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+// The hardware cluster barrier has no bounded form; both CTAs of a pair reach it unconditionally (prologue and
+// teardown only; after an expired wait every role of both CTAs falls through to the teardown).
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }

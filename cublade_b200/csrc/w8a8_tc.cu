@@ -277,6 +277,10 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+// The hardware cluster barrier has no bounded form; it is safe here because both CTAs of a pair reach it
+// unconditionally: it sits only in the prologue (before any wait) and in the teardown, which every role of both CTAs
+// reaches -- an expired mbarrier wait raises the CTA's abort flag, after which all of its loops (and, through the
+// barriers they stop feeding, the peer's bounded waits) fall through to the teardown.
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }

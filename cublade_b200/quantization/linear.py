@@ -13,11 +13,12 @@ import torch
 import torch.nn as nn
 
 from ..bindings.w8a16 import gather_columns, w8a16_linear
+from ._devcache import DeviceBufferCache
 from .outlier_utils import separate_outliers
 from .quantizers import quantize_tensor
 
 
-class cuBladeW8A16LinearLayer(nn.Module):
+class cuBladeW8A16LinearLayer(DeviceBufferCache, nn.Module):
     def __init__(self, in_features, out_features, bias=True, dtype=torch.bfloat16, handle_outliers=False,
                  outlier_threshold=6.0):
         super().__init__()
@@ -62,29 +63,6 @@ class cuBladeW8A16LinearLayer(nn.Module):
         scale_1d = qt.scale.squeeze()
         assert scale_1d.ndim == 1 and scale_1d.numel() == self.out_features
         self.scales.copy_(scale_1d.to(self.scales.dtype))
-
-    def _on(self, name: str, dev: torch.device, dtype=None) -> torch.Tensor:
-        """Buffer ``name`` on ``dev`` (and cast to ``dtype``), cached while the buffer object is unchanged."""
-        src = getattr(self, name)
-        if src.device == dev and (dtype is None or src.dtype == dtype) and src.is_contiguous():
-            return src
-        key = (name, dev, dtype)
-        hit = self._dev_cache.get(key)
-        if hit is not None and hit[0] is src and hit[1] == src._version:
-            return hit[2]
-        moved = src.to(device=dev, dtype=dtype if dtype is not None else src.dtype).contiguous()
-        self._dev_cache[key] = (src, src._version, moved)
-        return moved
-
-    def _cached(self, key, sources, build):
-        """Derived device tensor ``key``, rebuilt when one of the ``sources`` buffers was replaced or written."""
-        stamp = tuple((id(t), t._version) for t in sources)
-        hit = self._dev_cache.get(key)
-        if hit is not None and hit[0] == stamp and all(a is b for a, b in zip(hit[1], sources)):
-            return hit[2]
-        made = build()
-        self._dev_cache[key] = (stamp, tuple(sources), made)
-        return made
 
     def _padded_weights(self, dev: torch.device, width: int) -> torch.Tensor:
         """``int8_weights`` on ``dev`` with zero columns appended up to ``width``.

@@ -12,9 +12,10 @@ import torch
 import torch.nn as nn
 
 from ..bindings.w4a16 import w4_quantize_rows, w4a16_linear
+from ._devcache import DeviceBufferCache
 
 
-class cuBladeW4A16LinearLayer(nn.Module):
+class cuBladeW4A16LinearLayer(DeviceBufferCache, nn.Module):
     def __init__(self, in_features, out_features, bias=True, dtype=torch.bfloat16):
         super().__init__()
         if in_features % 8 != 0:
@@ -24,6 +25,7 @@ class cuBladeW4A16LinearLayer(nn.Module):
         self.register_buffer("int4_weights", torch.zeros(out_features, in_features // 2, dtype=torch.uint8))
         self.register_buffer("scales", torch.ones(out_features, dtype=dtype))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype)) if bias else None
+        self._dev_cache = {}
 
     @torch.no_grad()
     def quantize(self, weight_fp: torch.Tensor):
@@ -41,8 +43,7 @@ class cuBladeW4A16LinearLayer(nn.Module):
         if x.shape[-1] != self.in_features:
             raise ValueError(f"cuBladeW4A16LinearLayer.forward: expected {self.in_features} input features, got {x.shape[-1]}")
         dev = x.device
-        wq = self.int4_weights if self.int4_weights.device == dev else self.int4_weights.to(dev)
-        ws = self.scales if self.scales.device == dev else self.scales.to(dev)
+        wq, ws = self._on("int4_weights", dev), self._on("scales", dev)  # cached device copies, no upload per call
         bias = None
         if self.bias is not None:
             bias = self.bias.detach()
@@ -50,5 +51,5 @@ class cuBladeW4A16LinearLayer(nn.Module):
         x2d = x.reshape(-1, self.in_features)
         if x2d.stride(-1) != 1:
             x2d = x2d.contiguous()
-        y2d = w4a16_linear(x2d, wq.contiguous(), ws.contiguous(), bias)
+        y2d = w4a16_linear(x2d, wq, ws, bias)
         return y2d.view(*x.shape[:-1], self.out_features)

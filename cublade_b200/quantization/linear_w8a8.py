@@ -16,11 +16,12 @@ import torch.nn as nn
 
 from ..bindings.cuda.quantize_int8 import quantize_per_axis_int8, quantize_per_channel_int8
 from ..bindings.w8a8 import w8a8_linear
+from ._devcache import DeviceBufferCache
 from .quantizers import quantize_tensor
 from .tensor import QuantizedTensor
 
 
-class cuBladeW8A8LinearLayer(nn.Module):
+class cuBladeW8A8LinearLayer(DeviceBufferCache, nn.Module):
     def __init__(self, in_features, out_features, bias=True, dtype=torch.bfloat16):
         super().__init__()
         self.in_features = in_features
@@ -28,6 +29,7 @@ class cuBladeW8A8LinearLayer(nn.Module):
         self.register_buffer("int8_weights", torch.empty(out_features, in_features, dtype=torch.int8))
         self.register_buffer("scales", torch.ones(out_features, dtype=dtype))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype)) if bias else None
+        self._dev_cache = {}
 
     @torch.no_grad()
     def quantize(self, weight_fp: torch.Tensor):
@@ -60,11 +62,10 @@ class cuBladeW8A8LinearLayer(nn.Module):
         if xq.shape[-1] != self.in_features:
             raise ValueError(f"cuBladeW8A8LinearLayer.forward: expected {self.in_features} input features, got {xq.shape[-1]}")
         dev = xq.device
-        wq = self.int8_weights if self.int8_weights.device == dev else self.int8_weights.to(dev)
-        ws = self.scales if self.scales.device == dev else self.scales.to(dev)
+        wq, ws = self._on("int8_weights", dev), self._on("scales", dev)  # cached device copies, no upload per call
         bias = None
         if self.bias is not None:
             bias = self.bias.detach()
             bias = (bias if bias.device == dev else bias.to(dev)).contiguous()
-        y2d = w8a8_linear(xq, xs, wq.contiguous(), ws.contiguous(), bias, out_dtype=dtype)
+        y2d = w8a8_linear(xq, xs, wq, ws, bias, out_dtype=dtype)
         return y2d.view(*lead, self.out_features)

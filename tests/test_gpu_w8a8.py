@@ -38,6 +38,22 @@ def test_binding_matches_oracle_bit_for_bit(M, N, K, bias, dtype):
     assert Nat.device_error_state() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 40000, 256), (300, 80000 + 128, 128), (1024, 24000, 192)])
+def test_pair_kernel_with_several_tiles_per_cta_pair(M, N, K):
+    """M >= 256 runs on pairs of CTAs (`tcgen05.mma.cta_group::2`): more 256-feature tiles than the 74 pairs of the
+    GPU, so every pair walks through several tiles (ring and accumulator phases wrap, the hardware cluster barrier is
+    reached once at the start and once at the end), with a ragged last tile in M and in N."""
+    from cublade_b200 import _native as Nat
+    from cublade_b200.bindings.w8a8 import w8a8_linear
+
+    dtype = torch.bfloat16
+    w, x, b, lay = _problem(M, N, K, dtype, M + N + K, True)
+    xq, xs = O.int8_quantize_rows(x)
+    y = w8a8_linear(xq.cuda(), xs.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda(), out_dtype=dtype)
+    assert_bits_equal(y, O.w8a8_forward(x, lay, b, xq=xq, xs=xs), "y")
+    assert Nat.device_error_state() == 0
+
+
 @pytest.mark.parametrize("M", [1, 16, 128, 2048])
 def test_layer_config4_shapes_and_accuracy(M):
     """N = 14336, K = 4096 (the W8A16 benchmark shape).  The layer must equal the oracle bit for bit and stay

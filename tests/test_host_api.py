@@ -83,6 +83,33 @@ def test_outlier_utilities():
     assert detect_outlier_columns(torch.ones(3, 3)) == []
 
 
+def test_outlier_utilities_equal_the_reference_module_on_random_weights():
+    """The reference's outlier_utils.py is pure torch: loaded by file path from a checkout beside this repository
+    (skipped where there is none) and compared call for call on random weights with planted > threshold entries."""
+    import importlib.util
+    from pathlib import Path
+
+    src = Path(__file__).resolve().parents[2] / "reference" / "cublade" / "quantization" / "outlier_utils.py"
+    if not src.exists():
+        pytest.skip("no reference checkout beside the repository")
+    spec = importlib.util.spec_from_file_location("ref_outlier_utils", src)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    g = torch.Generator().manual_seed(17)
+    for shape, thr, planted in (((64, 96), 6.0, 5), ((128, 40), 3.5, 0), ((7, 512), 6.0, 31), ((16, 16), 0.5, 16)):
+        w = torch.randn(*shape, generator=g)
+        cols = torch.randperm(shape[1], generator=g)[:planted]
+        rows = torch.randint(0, shape[0], (planted,), generator=g)
+        w[rows, cols] = (thr + 1.0) * torch.where(torch.rand(planted, generator=g) < 0.5, -1.0, 1.0)
+        assert detect_outlier_columns(w, thr) == ref.detect_outlier_columns(w, thr)
+        mine, theirs = separate_outliers(w, thr), ref.separate_outliers(w, thr)
+        assert mine[2] == theirs[2] and mine[3] == theirs[3]
+        assert torch.equal(mine[0], theirs[0]) and torch.equal(mine[1], theirs[1])
+        explicit = cols.tolist()[::-1]
+        a, b = split_weights_by_outliers(w, explicit), ref.split_weights_by_outliers(w, explicit)
+        assert a[2] == b[2] and a[3] == b[3] and torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
 class _Recorder(nn.Module):
     """Stand-in quantized layer that records how replace_linear_layers drives it."""
 

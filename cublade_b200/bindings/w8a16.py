@@ -51,7 +51,8 @@ def w8a16_linear(
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``y = (x2d @ int8_weights.T) * scales [+ x_outlier @ w_outlier.T] [+ bias]`` with fp32
-    accumulation and one final rounding to ``x2d.dtype``.
+    accumulation, rounded to ``x2d.dtype`` after the GEMM, after the scales, after the outlier product and after the
+    bias -- the places where the reference's chain of kernels rounds (cublade/quantization/linear.py:97-135).
 
     Args:
         x2d: ``[M, K]`` float16 / bfloat16 CUDA tensor (rows may be strided).

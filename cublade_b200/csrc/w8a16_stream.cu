@@ -18,7 +18,7 @@
 //
 // Four warps of a CTA split K four ways for one 16-row tile and reduce through
 // shared memory; the epilogue applies the per-row scale, adds the 16-bit side
-// product over the outlier columns and the bias, rounds once, and stores.
+// product over the outlier columns and the bias, rounds in the reference's places, and stores.
 
 #include "launch.h"
 #include "pack.cuh"

@@ -37,7 +37,7 @@
 // (fewer tiles than SMs) splits its tiles along K over the idle CTAs: every split stores its fp32
 // partial accumulator to its own slab of the workspace, and a small second kernel adds the slabs
 // of a tile in a fixed order and applies the ordinary epilogue (scale, outlier side product, bias,
-// one rounding).  Nobody waits for anybody, nothing is zeroed, and the result is deterministic.
+// each rounded as the reference rounds).  Nobody waits for anybody, nothing is zeroed, and the result is deterministic.
 //
 // No TMA multicast, no clusters, no peer memory.  Every mbarrier wait is bounded: on expiry the
 // kernel raises an error flag in global memory, every role leaves its loop, TMEM is released and
@@ -240,7 +240,7 @@ __device__ __noinline__ void epilogue_split(const TcParams& p, uint32_t taddr, u
 }
 
 // Second kernel of a call whose last round was split: one warp per output row of a split tile adds
-// the slabs in split order and finishes the row (scale, outlier side product, bias, one rounding).
+// the slabs in split order and finishes the row (scale, outlier side product, bias, each rounded as the reference rounds).
 template <typename A>
 __global__ void __launch_bounds__(256) w8a16_tc_fixup_kernel(const __grid_constant__ TcParams p, int grid_main) {
     pdl_wait();  // the slabs come from the kernel ahead

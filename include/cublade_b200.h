@@ -127,7 +127,9 @@ int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float*
  * elements apart.  wq [N, K] int8 row-major.  scales [N] of scales_dtype.
  * bias [N] of bias_dtype or NULL.  xo [M, KO] / wo [N, KO] (act_dtype, KO may
  * be 0 with NULL pointers) carry the LLM.int8 outlier columns kept in 16-bit.
- * fp32 accumulation, one rounding to act_dtype at the end.
+ * fp32 accumulation; the result is rounded to act_dtype where the reference's chain of kernels materialises a
+ * tensor: r(r(acc) * r(scales)), then r(. + r(outlier product)), then r(. + r(bias)) -- linear.py:97-135 -- so it
+ * equals the reference's output up to the order of the fp32 accumulation.
  * path: 0 auto, 1 weight-streaming kernel, 2 tcgen05 CTA-pair kernel, 3 tcgen05 single-CTA kernel.
  * ------------------------------------------------------------------------ */
 size_t cb_w8a16_workspace_bytes(int64_t M, int64_t N, int64_t K);

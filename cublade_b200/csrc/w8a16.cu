@@ -27,7 +27,8 @@ cudaError_t launch_w8a16(const W8A16Args& a, int path, cudaStream_t s) {
     if (path == 2) return w8a16_tc_pair_supported(a) ? launch_w8a16_tc_pair(a, s) : cudaErrorNotSupported;
     if (path == 3) return w8a16_tc_supported(a) ? launch_w8a16_tc(a, s) : cudaErrorNotSupported;
     if (a.M >= kTcMinM) {
-        // measured on B200: the single-CTA kernel is ahead of the CTA-pair kernel at every M tried
+        // measured on B200 (N = 14336, K = 4096): the single-CTA kernel is ahead of the CTA-pair kernel at every M tried
+        // (M = 416 / 2048 / 8192: 51 / 200 / 906 us against 55 / 211 / 932 us)
         if (w8a16_tc_supported(a)) return launch_w8a16_tc(a, s);
         if (w8a16_tc_pair_supported(a)) return launch_w8a16_tc_pair(a, s);
     }

@@ -1,39 +1,35 @@
-// W8A16 linear for tall activations, CTA-pair version: tcgen05.mma.cta_group::2 over a cluster
-// of two CTAs (two SMs), M = 256 weight rows x N <= 256 activation rows per pair tile.
+// W8A16 linear for tall activations on PAIRS of CTAs: tcgen05.mma.cta_group::2 over a cluster of two CTAs
+// (two SMs).  A pair's work item is 256 output features x two activation tiles of up to 208 rows.
 //
-//   y[m, n] = (sum_k x[m, k] * wq[n, k]) * scale[n] + sum_j xo[m, j] * wo[n, j] + bias[n]
+//   y[m, n] = r(r(sum_k x[m, k] * wq[n, k]) * r(scale[n])) (+ r(bias[n]), rounded)      r = round to the activation type
 //
-// Same structure and orientation as the single-CTA kernel (w8a16_tc.cu: weights are UMMA
-// operand A, activations operand B, accumulator D[n (lane), m (column)] double-buffered in TMEM),
-// with the pair sharing operand B: CTA r of the pair
-//   * owns weight rows [256 tn + 128 r, +128): loads their int8 tile by TMA, widens it to 16-bit
-//     in its own shared memory, holds their accumulator rows in its own TMEM and runs their
-//     epilogue;
-//   * loads only HALF of the activation tile (rows [tile_x tx + r tile_x/2, + tile_x/2)); the
-//     tensor cores of both SMs read both halves.
-// Per SM and per 128 x tile_x x 64 block of MACs this moves 8 KiB + tile_x * 64 B through
-// L2 -> shared memory instead of 8 KiB + tile_x * 128 B.
+// Why pairs.  The single-CTA kernel (w8a16_tc.cu) is bound by what one SM pulls out of L2 per k-block: the int8
+// weight tile (8 KB) and the activation tile (128 B per row).  With cta_group::2 the tensor cores of both SMs
+// read operand B (the activations) from BOTH CTAs' shared memory, so each CTA loads only HALF of every activation
+// tile: 2 x 13 KB + 8 KB = 34 KB per k-block for 128 features x 416 rows, against 61 KB in the single-CTA
+// two-tile mode.  Each CTA keeps what is its own: the int8 tile of its 128 weight rows (TMA), their widening
+// into its own tensor memory (operand A is read from tensor memory, tcgen05.st by the converter warps), their
+// two accumulators (2 x 208 columns + 3 A stages x 32 = 512 columns) and their epilogue.
 //
-// A pipeline stage is 128 wide in k (two 64-wide swizzle atoms), so every barrier probe, TMA issue
-// and commit is paid once per 8 MMAs: with 64-wide stages the single-thread roles (a probe costs
-// ~130 cycles even on a completed phase, a TMA issue ~100) set the pace, not the tensor core.
-// Roles per CTA (23 warps): warp 0 TMA producer for activations, warp 22 TMA producer for int8
-// weights (+ L2 prefetch six stages ahead), warp 1 MMA issuer (leader) / relay (peer), warps 2-5
-// epilogue, warps 6-21 converters.
+// Roles per CTA (15 warps): warp 0 TMA producer of this CTA's activation halves; warp 14 TMA producer of its int8
+// tiles (+ L2 prefetch); warp 1 MMA issuer (leader CTA only: one thread issues every tcgen05.mma of the pair);
+// warps 2-5 epilogue; warps 6-13 converters, two groups of four warps on alternate k-blocks.
 //
-// Cross-CTA signalling (no TMA multicast anywhere): every TMA load and every converter arrival
-// completes on a barrier of the CTA that owns the data; in the peer CTA two relay lanes forward
-// "activation half landed" and "weight rows widened" to the leader as ONE remote mbarrier.arrive
-// each per stage; the leader's single MMA thread issues every tcgen05.mma and signals "slot free" /
-// "accumulator ready" to both CTAs with tcgen05.commit ... .multicast::cluster; the peer's
-// epilogue warps arrive remotely on the leader's "accumulator drained" barrier.
-// Every wait is bounded (see tc_common.cuh); on expiry the error flag is raised, all roles leave
-// their loops, the pair meets at a cluster barrier, TMEM is released and the kernel returns.
+// Signalling.  Ring slot s of the LEADER carries the "full" barrier the MMA thread waits on: the activation
+// loads of both CTAs complete on it (the .cta_group::2 form of the TMA load may name a barrier of the peer CTA;
+// no multicast is involved, every load is a plain per-CTA load) and the converter warps of both CTAs arrive on
+// it (one arrival per CTA and k-block, after the group's four warps met at a named barrier).  The int8 tile of a CTA completes on a local
+// barrier its own converters wait on.  The leader frees a slot in both CTAs, and publishes the finished
+// accumulators to both, with tcgen05.commit ... multicast::cluster (an mbarrier arrive, not a load); the epilogue
+// warps of both CTAs arrive on the leader's "accumulator drained" barriers.  The accumulators are not
+// double-buffered: the next item's MMAs into an accumulator wait until both CTAs have drained it.
+// Every wait is bounded (tc_common.cuh); on expiry the error flag is raised, all roles leave their loops, the
+// pair meets at the cluster barrier, tensor memory is released and the kernel returns.
+//
+// Not served here (the single-CTA kernel takes these): outlier columns, K % 16 != 0, fewer than 256 features.
 
 #include "tc_common.cuh"
 
-#include <cstdio>
-#include <cstdlib>
 #include <mutex>
 
 namespace cb {
@@ -42,30 +38,53 @@ namespace {
 
 using namespace tc;
 
-constexpr int kMaxTileX = 256;  // activation rows per pair tile = UMMA N (multiple of 16)
-// A pipeline stage covers kSub consecutive 64-wide k-blocks (one 128-byte swizzle atom each): every
-// barrier probe (~130 cycles even when complete), TMA issue (~100) and commit is paid once per
-// stage, and with 64-wide stages those per-stage costs of the single-thread roles, not the tensor
-// core, set the pace of the main loop.
-constexpr int kSub = 2;
-constexpr int kStageK = kSub * kBlockK;  // 128
-constexpr int kStagesA = 3;     // converted weight stages (kSub x 16 KiB each)
-constexpr int kStagesW8 = 2;    // int8 weight stages (kSub x 8 KiB each)
-constexpr int kMaxStages = 8;   // activation half stages (kSub x <= 16 KiB each)
-constexpr int kConvWarps = 16;
-constexpr int kConvGroupWarps = 16; // converter warps per group (one group: all warps share every stage)
+constexpr int kTileN = 128;        // weight rows per CTA
+constexpr int kMaxTileX = 208;     // rows of one activation tile = UMMA N (a multiple of 16)
+constexpr int kHalves = 2;         // activation tiles per work item
+constexpr int kStages = 6;         // ring slots (activation halves + int8 tile)
+constexpr int kTmemAStages = 3;    // widened-weight stages in tensor memory: slot s uses stage s % 3
+constexpr int kConvWarps = 8;
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (3 + kEpiWarps + kConvWarps) * 32;  // + TMA(x), MMA/relay, TMA(w8)
-constexpr int kW8Warp = 2 + kEpiWarps + kConvWarps;         // last warp: int8 weight producer
+constexpr int kThreads = (3 + kEpiWarps + kConvWarps) * 32;
+constexpr int kW8Warp = 2 + kEpiWarps + kConvWarps;  // 14: int8 weight producer
 constexpr int kTmemCols = 512;
-constexpr uint32_t kBytesASub = kUmmaM * kBlockK * 2;  // 16384: one 128-row x 64-k converted sub-tile
-constexpr uint32_t kBytesA = kSub * kBytesASub;        // 32768 per stage
-constexpr uint32_t kBytesW8 = kUmmaM * kStageK;        // 16384 per stage: 128 rows x 128 int8
-constexpr uint32_t kPeerMask = 0xFEFFFFFFu;         // shared::cluster address -> same offset in CTA rank 0
-constexpr uint32_t kSmemLimit = 232448;             // 227 KiB opt-in shared memory per CTA
-// barriers: full_x[8], empty_x[8], peer_x[8], full_a[3], empty_a[3], peer_a[3], full_w8[4], empty_w8[4], tmem_full[2], tmem_empty[2]
-constexpr uint32_t kNumBars = 3 * kMaxStages + 3 * kStagesA + 2 * kStagesW8 + 4;
-constexpr uint32_t kTailBytes = kNumBars * 8 + 16;
+constexpr int kAccStride = kMaxTileX;       // columns between the two accumulators
+constexpr int kACol = kHalves * kMaxTileX;  // first column of the A stages
+constexpr int kAColsPerStage = kBlockK / 2; // two 16-bit k per 32-bit column
+constexpr int kPfBlocks = 4;                // k-blocks of weights per L2 prefetch
+constexpr uint32_t kBytesXHalf = (kMaxTileX / 2) * kBlockK * 2;  // 13312: this CTA's half of one activation tile
+constexpr uint32_t kBytesX = kHalves * kBytesXHalf;              // 26624 per slot
+constexpr uint32_t kBytesW8 = kTileN * kBlockK;                  // 8192 per slot
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // shared::cluster address -> same offset in CTA rank 0
+static_assert(kACol + kTmemAStages * kAColsPerStage <= kTmemCols, "tensor memory map");
+static_assert(kBytesXHalf % 1024 == 0, "swizzle atoms need 1024-byte aligned tiles");
+
+struct Smem {
+    static constexpr uint32_t x = 0;
+    static constexpr uint32_t w8 = x + kStages * kBytesX;
+    static constexpr uint32_t bars = w8 + kStages * kBytesW8;
+    // full[kStages], empty[kStages], full_w8[kStages], tmem_full, tmem_empty[2]
+    static constexpr uint32_t n_bars = 3 * kStages + 3;
+    static constexpr uint32_t tmem_slot = bars + n_bars * 8;
+    static constexpr uint32_t abort_flag = tmem_slot + 4;
+    static constexpr uint32_t total = abort_flag + 4;
+};
+constexpr uint32_t kSmemBytes = Smem::total + 1024;
+static_assert(kSmemBytes <= 232448, "shared memory map");
+
+struct PairParams {
+    int64_t M, N, K;
+    const void* scales;
+    int scales_dtype;
+    const void* bias;
+    int bias_dtype;
+    void* y;
+    int64_t ldy;
+    int tile_x;   // rows of one activation tile (multiple of 16, <= 208)
+    int tiles_x;  // ceil(M / (2 * tile_x))
+    int tiles_n;  // ceil(N / 256)
+    unsigned int* error_flag;
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -81,115 +100,83 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerMask) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx_leader(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar & kPeerMask), "r"(bytes) : "memory");
+}
+// TMA tile load into THIS CTA's shared memory whose bytes are counted on the leader's barrier (no multicast)
+__device__ __forceinline__ void tma_load_2d_to_leader_bar(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar & kPeerMask)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
-                 : "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                              uint32_t accumulate) {
+// M = 256 over the pair, operand A (this CTA's 128 rows x 16 k) from tensor memory, operand B from both CTAs'
+// shared memory (each holds N / 2 rows at the descriptor's offset)
+__device__ __forceinline__ void umma_f16_pair_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // arrive (once all prior MMAs of this thread retired) on the barrier at this offset in BOTH CTAs
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(bar), "h"((uint16_t)3)
-        : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
-// instruction descriptor for the pair: M = 256 (128 rows per CTA), N = n, fp32 accumulate, K-major operands
+// kind::f16, fp32 accumulate, both operands K-major, M = 256 over the pair, N = n
 __device__ __forceinline__ uint32_t make_idesc_pair(bool bf16, uint32_t n) {
     const uint32_t fmt = bf16 ? 1u : 0u;
     return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
-// Warp-collective bounded wait: lane 0 polls, the result is broadcast.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, int lane) {
-    int ok = 1;
-    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
-
-struct PairParams {
-    int64_t M, N, K;
-    const void* scales;
-    int scales_dtype;
-    const void* bias;
-    int bias_dtype;
-    const void* xo;
-    const void* wo;
-    int64_t KO, ldxo;
-    void* y;
-    int64_t ldy;
-    int tile_x;    // activation rows per pair tile (multiple of 16, <= 256); each CTA loads tile_x / 2
-    int tiles_x;   // ceil(M / tile_x)
-    int tiles_n;   // ceil(N / 256)
-    int stages;    // depth of the activation ring
-    uint32_t x_stage_bytes;  // kSub sub-tiles
-    uint32_t x_sub_bytes;    // one sub-tile (half_x rows x 128 B, rounded up to 1 KiB)
-    unsigned int* error_flag;
-    int debug;  // development builds only: 1 skip the widening, 2 skip the MMAs, 4 skip the proxy fence, 8 no L2 prefetch
-};
 
 template <typename A>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                     const PairParams p) {
+                     const __grid_constant__ CUtensorMap map_pf, const __grid_constant__ PairParams p) {
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t rank = cluster_ctarank();   // 0 = leader
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t stages = (uint32_t)p.stages;
-    const uint32_t sa = base;                                   // converted weights, kStagesA x 16 KiB
-    const uint32_t sw8 = sa + kStagesA * kBytesA;               // int8 weights, kStagesW8 x 8 KiB
-    const uint32_t sx = sw8 + kStagesW8 * kBytesW8;             // activation halves, stages x x_stage_bytes
-    const uint32_t bars = sx + stages * p.x_stage_bytes;
-    // full_x / full_a are LOCAL in each CTA (own activation half landed / own weight rows widened);
-    // the peer's relay lanes forward each as ONE remote arrive on the leader's peer_x / peer_a.
-    // empty_x / empty_a are signalled in both CTAs by the leader's multicast tcgen05.commit.
-    const uint32_t full_x = bars, empty_x = full_x + 8 * kMaxStages, peer_x = empty_x + 8 * kMaxStages;
-    const uint32_t full_a = peer_x + 8 * kMaxStages, empty_a = full_a + 8 * kStagesA, peer_a = empty_a + 8 * kStagesA;
-    const uint32_t full_w8 = peer_a + 8 * kStagesA, empty_w8 = full_w8 + 8 * kStagesW8;
-    const uint32_t tmem_full = empty_w8 + 8 * kStagesW8, tmem_empty = tmem_full + 16;
-    const uint32_t tmem_slot_addr = tmem_empty + 16;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + (tmem_slot_addr - base));
-    volatile uint32_t* abort_flag = tmem_slot + 1;
+    const uint32_t sx = base + Smem::x, sw8 = base + Smem::w8;
+    const uint32_t full = base + Smem::bars, empty = full + 8 * kStages, full_w8 = empty + 8 * kStages;
+    const uint32_t tmem_full = full_w8 + 8 * kStages, tmem_empty = tmem_full + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + Smem::tmem_slot);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gbase + Smem::abort_flag);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (int)((p.K + kBlockK - 1) / kBlockK);
+    const int total_items = p.tiles_x * p.tiles_n;  // items of 256 features x 2 activation tiles
     const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
-    const int num_kb = (int)((p.K + kStageK - 1) / kStageK);  // pipeline stages per tile
-    const int total_tiles = p.tiles_x * p.tiles_n;
-    const int half_x = p.tile_x >> 1;
-    const uint32_t sub_bytes = (uint32_t)half_x * kBlockK * 2;     // one activation sub-tile
-    const uint32_t half_bytes = kSub * sub_bytes;
+    const int half_rows = p.tile_x / 2;
+    const uint32_t half_bytes = (uint32_t)half_rows * kBlockK * 2;  // one CTA's half of one activation tile, one k-block
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kMaxStages; ++i) {
-            mbar_init(full_x + 8 * i, 1);
-            mbar_init(empty_x + 8 * i, 1);
-            mbar_init(peer_x + 8 * i, 1);
+        // full (used on the leader): one arrive.expect_tx per CTA + one arrive per CTA for its converter group;
+        // empty / tmem_full: the leader's multicast commit; tmem_empty (leader): the epilogue warps of both CTAs
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(full + 8 * i, 2 + 2);
+            mbar_init(empty + 8 * i, 1);
+            mbar_init(full_w8 + 8 * i, 1);
         }
-        for (int i = 0; i < kStagesA; ++i) {
-            mbar_init(full_a + 8 * i, kConvGroupWarps);
-            mbar_init(empty_a + 8 * i, 1);
-            mbar_init(peer_a + 8 * i, 1);
-        }
-        for (int i = 0; i < kStagesW8; ++i) { mbar_init(full_w8 + 8 * i, 1); mbar_init(empty_w8 + 8 * i, kConvGroupWarps); }
-        for (int i = 0; i < 2; ++i) { mbar_init(tmem_full + 8 * i, 1); mbar_init(tmem_empty + 8 * i, 2 * kEpiWarps); }
+        mbar_init(tmem_full, 1);
+        for (int i = 0; i < 2; ++i) mbar_init(tmem_empty + 8 * i, 2 * kEpiWarps);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_x);
         prefetch_tmap(&map_w);
+        prefetch_tmap(&map_pf);
     }
-    if (warp == 1) tmem_alloc_pair(tmem_slot_addr, kTmemCols);
+    if (warp == 1) tmem_alloc_pair(base + Smem::tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across
@@ -197,43 +184,41 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------ TMA producer, activations (both CTAs) ------------------------------
-        // The two producers are separate warps: a barrier probe costs ~130 cycles and a TMA issue
-        // ~100, so one thread doing both rings cannot stay ahead of the tensor core.
+        // ------------------------------ TMA producer: this CTA's halves of the two activation tiles ------------------------------
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
-                const int row_x = (t % p.tiles_x) * p.tile_x + (int)rank * half_x;
+            for (int t = pair; t < total_items && ok; t += num_pairs) {
+                const int row_x = (t % p.tiles_x) * p.tile_x * kHalves + (int)rank * half_rows;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    { ok = mbar_wait(empty_x + 8 * s, ph ^ 1u, abort_flag); }
+                    ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);  // local copy: freed by the leader's multicast commit
                     if (!ok) break;
-                    { mbar_expect_tx(full_x + 8 * s, half_bytes);
-#pragma unroll
-                    for (int u = 0; u < kSub; ++u)
-                        tma_load_2d(sx + s * p.x_stage_bytes + u * p.x_sub_bytes, &map_x, kb * kStageK + u * kBlockK, row_x,
-                                    full_x + 8 * s); }
-                    if (++s == stages) { s = 0; ph ^= 1u; }
+                    mbar_expect_tx_leader(full + 8 * s, kHalves * half_bytes);
+                    tma_load_2d_to_leader_bar(sx + s * kBytesX, &map_x, kb * kBlockK, row_x, full + 8 * s);
+                    // second activation tile of the item (rows beyond M arrive as zeros)
+                    tma_load_2d_to_leader_bar(sx + s * kBytesX + kBytesXHalf, &map_x, kb * kBlockK, row_x + p.tile_x, full + 8 * s);
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == kW8Warp) {
-        // ------------------------------ TMA producer, int8 weights (both CTAs) ------------------------------
+        // ------------------------------ TMA producer: this CTA's int8 weight tile (local barrier) ------------------------------
         if (lane == 0) {
+            constexpr int kAhead = 12;  // k-blocks of weights requested into L2 ahead of their TMA load
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            constexpr int kAhead = 6;  // stages of int8 weights requested into L2 ahead of their TMA load
-            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
-                const int row_w = (t / p.tiles_x) * 256 + (int)rank * kUmmaM;
-                const int row_w_next = ((t + num_pairs) / p.tiles_x) * 256 + (int)rank * kUmmaM;
+            for (int t = pair; t < total_items && ok; t += num_pairs) {
+                const int row_w = (t / p.tiles_x) * 256 + (int)rank * kTileN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (kb + kAhead < num_kb) tma_prefetch_l2_2d(&map_w, (kb + kAhead) * kStageK, row_w);
-                    else if (t + num_pairs < total_tiles) tma_prefetch_l2_2d(&map_w, (kb + kAhead - num_kb) * kStageK, row_w_next);
-                    { ok = mbar_wait(empty_w8 + 8 * s, ph ^ 1u, abort_flag); }
+                    if ((kb & (kPfBlocks - 1)) == 0 && kb + kAhead < num_kb)
+                        tma_prefetch_l2_2d(&map_pf, (kb + kAhead) * kBlockK, row_w);
+                    // the int8 staging buffer of a slot is free when the slot is: the MMAs that retired consumed what
+                    // the converters made of it
+                    ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag);
                     if (!ok) break;
-                    { mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
-                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kStageK, row_w, full_w8 + 8 * s); }
-                    if (++s == kStagesW8) { s = 0; ph ^= 1u; }
+                    mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
+                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, row_w, full_w8 + 8 * s);
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -241,180 +226,140 @@ w8a16_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         // ------------------------------ MMA issuer (leader CTA only) ------------------------------
         if (rank == 0 && lane == 0) {
             const uint32_t idesc = make_idesc_pair(Widen<A>::kBf16, (uint32_t)p.tile_x);
-            // Ring positions are kept incrementally (no divisions), and the four barriers of a
-            // k-block are probed back to back before any result is used: a probe costs ~130 cycles
-            // even when the phase is already complete, and this thread's loop is the critical path.
-            uint32_t sx_i = 0, phx = 0, sa_i = 0, pha = 0, it = 0;
-            bool ok = true, pre = false;
-            for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
-                const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
-                { ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, abort_flag); }  // both epilogues drained it
-                if (!ok) break;
-                const uint32_t d_tmem = tmem_base + acc * kMaxTileX;
+            uint32_t s = 0, ph = 0, it = 0;
+            bool ok = true;
+            for (int t = pair; t < total_items && ok; t += num_pairs, ++it) {
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    {
-                        // `pre` holds the result of the probes issued one stage ago (they overlap the
-                        // MMA issue of the previous stage); only on a miss does the thread block here.
-                        if (!pre) {
-                            const bool r0 = mbar_try(full_a + 8 * sa_i, pha), r1 = mbar_try(peer_a + 8 * sa_i, pha);
-                            const bool r2 = mbar_try(full_x + 8 * sx_i, phx), r3 = mbar_try(peer_x + 8 * sx_i, phx);
-                            ok = (r0 || mbar_wait(full_a + 8 * sa_i, pha, abort_flag)) &&
-                                 (r1 || mbar_wait(peer_a + 8 * sa_i, pha, abort_flag)) &&
-                                 (r2 || mbar_wait(full_x + 8 * sx_i, phx, abort_flag)) &&
-                                 (r3 || mbar_wait(peer_x + 8 * sx_i, phx, abort_flag));
-                        }
-                    }
+                    ok = mbar_spin(full + 8 * s, ph, abort_flag);  // bytes and converter arrivals come from both CTAs
                     if (!ok) break;
                     tc_fence_after();
-                    // ring positions of the NEXT stage, probed now, consumed after this stage is issued
-                    uint32_t nsa = sa_i + 1, npha = pha, nsx = sx_i + 1, nphx = phx;
-                    if (nsa == kStagesA) { nsa = 0; npha ^= 1u; }
-                    if (nsx == stages) { nsx = 0; nphx ^= 1u; }
-                    const bool n0 = mbar_try(full_a + 8 * nsa, npha), n1 = mbar_try(peer_a + 8 * nsa, npha);
-                    const bool n2 = mbar_try(full_x + 8 * nsx, nphx), n3 = mbar_try(peer_x + 8 * nsx, nphx);
-#pragma unroll
-                    for (int u = 0; u < kSub; ++u) {
-                        const uint64_t adesc = make_kmajor_sw128_desc(sa + sa_i * kBytesA + u * kBytesASub);
-                        const uint64_t bdesc = make_kmajor_sw128_desc(sx + sx_i * p.x_stage_bytes + u * p.x_sub_bytes);
-#pragma unroll
-                        for (int k = 0; k < kBlockK / 16; ++k)
-                            umma_f16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                                          (kb > 0 || u > 0 || k > 0) ? 1u : 0u);
+                    const uint32_t a_tmem = tmem_base + kACol + (s % (uint32_t)kTmemAStages) * kAColsPerStage;
+                    const uint64_t bdesc0 = make_kmajor_sw128_desc(sx + s * kBytesX);
+                    const uint64_t bdesc1 = make_kmajor_sw128_desc(sx + s * kBytesX + kBytesXHalf);
+                    if (kb == 0) {  // both CTAs' epilogues have drained the first accumulator of the previous item
+                        ok = mbar_spin(tmem_empty, (it & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
                     }
-                    umma_commit_pair(empty_a + 8 * sa_i);  // frees the slots in both CTAs once these MMAs retire
-                    umma_commit_pair(empty_x + 8 * sx_i);
-                    pre = n0 && n1 && n2 && n3;
-                    sa_i = nsa; pha = npha; sx_i = nsx; phx = nphx;
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k)  // 16 k = 8 columns of A, 32 bytes of every B row
+                        umma_f16_pair_tmem_a(tmem_base, a_tmem + (uint32_t)(8 * k), bdesc0 + (uint64_t)(2 * k), idesc,
+                                             (kb > 0 || k > 0) ? 1u : 0u);
+                    if (kb == 0) {
+                        ok = mbar_spin(tmem_empty + 8, (it & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k)  // the same widened weights against the second activation tile
+                        umma_f16_pair_tmem_a(tmem_base + kAccStride, a_tmem + (uint32_t)(8 * k), bdesc1 + (uint64_t)(2 * k), idesc,
+                                             (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(empty + 8 * s);  // the slot is free in both CTAs once these MMAs retire
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit_pair(tmem_full + 8 * acc);
-            }
-        } else if (rank == 1 && lane < 2) {
-            // relays (two lanes, one per ring): when this CTA's activation half has landed (lane 0)
-            // or its weight rows are widened (lane 1), tell the leader with ONE remote arrive
-            const uint32_t depth = lane == 0 ? stages : (uint32_t)kStagesA;
-            const uint32_t local = lane == 0 ? full_x : full_a, remote = lane == 0 ? peer_x : peer_a;
-            const int64_t total_kb = pair < total_tiles ? (int64_t)((total_tiles - 1 - pair) / num_pairs + 1) * num_kb : 0;
-            uint32_t s = 0, ph = 0;
-            for (int64_t i = 0; i < total_kb; ++i) {
-                bool ok;
-                { ok = mbar_wait(local + 8 * s, ph, abort_flag); }
-                if (!ok) break;
-                mbar_arrive_leader(remote + 8 * s);
-                if (++s == depth) { s = 0; ph ^= 1u; }
+                umma_commit_pair(tmem_full);  // both accumulators complete -> the epilogues of both CTAs
             }
         }
     } else if (warp < 2 + kEpiWarps) {
-        // ------------------------------ epilogue (both CTAs, own 128 rows) ------------------------------
-        const int quarter = warp & 3;
-        const A* xo = static_cast<const A*>(p.xo);
-        const A* wo = static_cast<const A*>(p.wo);
-        A* y = static_cast<A*>(p.y);
+        // ------------------------------ epilogue (each CTA: its own 128 features, both activation tiles) ------------------------------
+        const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes 32 * (warp % 4) .. + 31
+        uint16_t* y = static_cast<uint16_t*>(p.y);
         uint32_t it = 0;
         bool ok = true;
-        for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
+        for (int t = pair; t < total_items && ok; t += num_pairs, ++it) {
             const int tx = t % p.tiles_x, tn = t / p.tiles_x;
-            const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
-            const int64_t n = (int64_t)tn * 256 + (int64_t)rank * kUmmaM + quarter * 32 + lane;
+            const int64_t n = (int64_t)tn * 256 + (int64_t)rank * kTileN + quarter * 32 + lane;
             const bool n_ok = n < p.N;
-            const float scale = n_ok ? ref_round<A>(load_scalar(p.scales, p.scales_dtype, n)) : 0.0f;
+            const float scale = n_ok ? load_scalar(p.scales, p.scales_dtype, n) : 0.0f;
             const bool has_bias = p.bias != nullptr;
-            const float bias = (n_ok && has_bias) ? ref_round<A>(load_scalar(p.bias, p.bias_dtype, n)) : 0.0f;
-            ok = warp_wait(tmem_full + 8 * acc, acc_ph, abort_flag, lane);
+            const float bias = (n_ok && has_bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+            const uint32_t scale2 = Widen<A>::pack2(scale, scale), bias2 = Widen<A>::pack2(bias, bias);  // rounded to A
+            {
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(tmem_full, it & 1u, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+            }
             if (!ok) break;
             tc_fence_after();
-            const int64_t m_base = (int64_t)tx * p.tile_x;
-            for (int c0 = 0; c0 < p.tile_x; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxTileX + (uint32_t)c0, r);
-                tmem_ld_wait();
+            for (int half = 0; half < kHalves; ++half) {
+                const int64_t m_base = ((int64_t)tx * kHalves + half) * p.tile_x;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)half * kAccStride;
+                for (int c0 = 0; c0 < p.tile_x && m_base + c0 < p.M; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    // rows of this block that exist; no control flow per row (predicated stores), two rows per step
+                    // in packed 16-bit arithmetic, every step rounded as the reference's chain of kernels rounds
+                    const int64_t rows_left = p.M - (m_base + c0);
+                    int nrows = rows_left < 32 ? (int)rows_left : 32;
+                    if (nrows > p.tile_x - c0) nrows = p.tile_x - c0;
+                    uint16_t* yrow = y + (m_base + c0) * p.ldy + n;
+                    const int64_t ystep = p.ldy;
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int64_t m = m_base + c0 + c;
-                    if (m >= p.M || c0 + c >= p.tile_x) break;  // uniform across the warp
-                    float v = ref_round<A>(ref_round<A>(__uint_as_float(r[c])) * scale);
-                    if (p.KO > 0 && n_ok) {
-                        const A* xrow = xo + m * p.ldxo;  // same address in every lane: broadcast load
-                        const A* wrow = wo + n * p.KO;
-                        float side = 0.0f;
-                        for (int j = 0; j < (int)p.KO; ++j)
-                            side = fmaf(Widen<A>::to_float(__ldg(xrow + j)), Widen<A>::to_float(__ldg(wrow + j)), side);
-                        v = ref_round<A>(v + ref_round<A>(side));
+                    for (int c = 0; c < 32; c += 2) {
+                        uint32_t v = Widen<A>::mul2(Widen<A>::pack2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2);
+                        v = has_bias ? Widen<A>::add2(v, bias2) : v;
+                        if (n_ok && c < nrows) yrow[(int64_t)c * ystep] = (uint16_t)(v & 0xffffu);
+                        if (n_ok && c + 1 < nrows) yrow[(int64_t)(c + 1) * ystep] = (uint16_t)(v >> 16);
                     }
-                    if (has_bias) v = ref_round<A>(v + bias);
-                    if (n_ok) y[m * p.ldy + n] = Widen<A>::from_float(v);
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(tmem_empty + 8 * half);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_leader(tmem_empty + 8 * acc);
         }
     } else if (warp < kW8Warp) {
-        // ------------------------------ converters (both CTAs, own 128 rows) ------------------------------
-        // Two groups of kConvGroupWarps warps take alternate stages, so the barrier probes, the
-        // shared-memory latency and the proxy fence of one stage overlap the arithmetic of the next.
-        const int lw = warp - (2 + kEpiWarps);
-        const int group = lw / kConvGroupWarps;
-        const int cid = (lw % kConvGroupWarps) * 32 + lane;  // 0 .. 255 within the group
-        uint32_t s_w = 0, ph_w = 0, s_a = 0, ph_a = 0;
-        auto advance = [&]() {
-            if (++s_w == kStagesW8) { s_w = 0; ph_w ^= 1u; }
-            if (++s_a == kStagesA) { s_a = 0; ph_a ^= 1u; }
-        };
-        if (group == 1) advance();
-        const int64_t total_st = pair < total_tiles ? (int64_t)((total_tiles - 1 - pair) / num_pairs + 1) * num_kb : 0;
+        // ------------------------------ converters: two groups of four warps on alternate k-blocks ------------------------------
+        // A thread owns weight row 32 * quarter + lane = its tensor-memory lane.  The int8 tile arrived with the 64-byte
+        // TMA swizzle, so the eight lanes of a quarter-warp hit eight different bank groups.
+        const int cw = warp - (2 + kEpiWarps);  // 0 .. 7
+        const uint32_t group = (uint32_t)(cw >> 2);
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t swz = (uint32_t)((row >> 1) & 3);  // chunk c of row r sits at c ^ ((r >> 1) & 3)
+        uint32_t s = 0, ph = 0, g = 0;
         bool ok = true;
-        {
-            for (int64_t st = group; st < total_st && ok; st += kConvWarps / kConvGroupWarps) {
-                {
+        for (int t = pair; t < total_items && ok; t += num_pairs) {
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                if (g == group) {
                     int okw = 1;
                     if (lane == 0) {
-                        const bool r0 = mbar_try(full_w8 + 8 * s_w, ph_w), r1 = mbar_try(empty_a + 8 * s_a, ph_a ^ 1u);
-                        okw = ((r0 || mbar_wait(full_w8 + 8 * s_w, ph_w, abort_flag)) &&
-                               (r1 || mbar_wait(empty_a + 8 * s_a, ph_a ^ 1u, abort_flag))) ? 1 : 0;
+                        okw = mbar_wait(full_w8 + 8 * s, ph, abort_flag) ? 1 : 0;
+                        // the tensor-memory stage is shared with the slot kTmemAStages back: its MMAs must have retired
+                        // (same ring round for the upper slots, the round before for the lower ones)
+                        if (okw) {
+                            const uint32_t back = s >= (uint32_t)kTmemAStages ? s - kTmemAStages : s + kTmemAStages;
+                            okw = mbar_wait(empty + 8 * back, s >= (uint32_t)kTmemAStages ? ph : ph ^ 1u, abort_flag) ? 1 : 0;
+                        }
                     }
-                    ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
-                }
-                if (!ok) break;
-                tc_fence_after();
-                {
+                    if (__shfl_sync(0xffffffffu, okw, 0) == 0) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_stage = s % (uint32_t)kTmemAStages;
+                    const uint32_t rbase = sw8 + s * kBytesW8 + (uint32_t)(row * 64);
 #pragma unroll
-                for (int pass = 0; pass < (kUmmaM * kStageK / 16) / (kConvGroupWarps * 32); ++pass) {
-                    // 16-byte chunk `id` of the int8 stage: 128-byte rows, chunk jc covers k = 16 jc .. +15
-                    const int id = pass * (kConvGroupWarps * 32) + cid;
-                    const int row = id >> 3, jc = id & 7, sub = jc >> 2, j = jc & 3;
-                    uint32_t c0, c1, c2, c3;
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-                                 : "r"(sw8 + s_w * kBytesW8 + (uint32_t)(id * 16)));
-                    uint32_t o[8];
-                    Widen<A>::four(c0, o[0], o[1]);
-                    Widen<A>::four(c1, o[2], o[3]);
-                    Widen<A>::four(c2, o[4], o[5]);
-                    Widen<A>::four(c3, o[6], o[7]);
-                    // 16-bit row = 128 bytes = eight 16-byte chunks; chunk c lives at c ^ (row % 8)
-                    const uint32_t rbase = sa + s_a * kBytesA + (uint32_t)sub * kBytesASub + (uint32_t)(row * 128);
-                    const uint32_t sw = (uint32_t)(row & 7);
-                    // The two sub-tiles sit 16 KiB apart (same banks), so lanes of sub-tile 1 store their
-                    // two chunks in the opposite order: each store instruction then touches eight
-                    // different 16-byte bank groups per quarter-warp.
-                    const bool swp = sub != 0;
-                    const uint32_t ca = (uint32_t)(2 * j + (swp ? 1 : 0)), cb2 = (uint32_t)(2 * j + (swp ? 0 : 1));
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rbase + ((ca ^ sw) << 4)),
-                                 "r"(swp ? o[4] : o[0]), "r"(swp ? o[5] : o[1]), "r"(swp ? o[6] : o[2]), "r"(swp ? o[7] : o[3])
-                                 : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(rbase + ((cb2 ^ sw) << 4)),
-                                 "r"(swp ? o[0] : o[4]), "r"(swp ? o[1] : o[5]), "r"(swp ? o[2] : o[6]), "r"(swp ? o[3] : o[7])
-                                 : "memory");
+                    for (int khalf = 0; khalf < 2; ++khalf) {
+                        uint32_t c[8];
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(c[4 * j]), "=r"(c[4 * j + 1]), "=r"(c[4 * j + 2]), "=r"(c[4 * j + 3])
+                                         : "r"(rbase + ((((uint32_t)(2 * khalf + j)) ^ swz) << 4)));
+                        uint32_t o[16];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) Widen<A>::four(c[j], o[2 * j], o[2 * j + 1]);
+                        tmem_st16(tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                      (uint32_t)(kACol + a_stage * kAColsPerStage + khalf * 16), o);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    // the group's four warps meet at a named barrier; one of them tells the leader (one remote arrive
+                    // per CTA and k-block: the tensor-memory writes are complete, nothing in memory has to be released)
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + (int)group) : "memory");
+                    if ((cw & 3) == 0 && lane == 0) mbar_arrive_leader(full + 8 * s);
                 }
-                }
-                fence_async_smem();  // generic-proxy stores -> visible to the tensor-core (async) proxy
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full_a + 8 * s_a);
-                    mbar_arrive(empty_w8 + 8 * s_w);
-                }
-                for (int q = 0; q < kConvWarps / kConvGroupWarps; ++q) advance();
+                g ^= 1u;
+                if (++s == kStages) { s = 0; ph ^= 1u; }
             }
         }
     }
@@ -463,25 +408,26 @@ bool make_map(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint64_
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Activation rows per pair tile: the multiple of 32 (<= 256) with the fewest wasted pair-slots over
-// the persistent schedule of ceil(M / tile) * ceil(N / 256) tiles on `pairs` CTA pairs.
-int pick_pair_tile_x(int64_t M, int64_t N, int pairs) {
-    const int64_t tiles_n = (N + 255) / 256;
-    int best = 256;
-    double best_cost = 1e30;
-    for (int tx = 256; tx >= 32; tx -= 16) {
-        const int64_t tiles = ((M + tx - 1) / tx) * tiles_n;
-        const int64_t waves = (tiles + pairs - 1) / pairs;
-        const double cost = (double)waves * (tx + 512);  // measured: a k-block costs nearly the same for every tile height
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = tx; }
-    }
-    return best;
-}
-
 }  // namespace
 
 unsigned int* w8a16_tc_error_word();  // w8a16_tc.cu
 
+// Rows of one activation tile (a multiple of 16, <= 208) and the modelled length of the schedule in units of
+// k-blocks x rows: ceil(M / (2 tile)) * ceil(N / 256) items on `pairs` CTA pairs.
+double w8a16_tc_pair_plan(int64_t M, int64_t N, int64_t K, int pairs, int* tile_x) {
+    const int64_t tiles_n = (N + 255) / 256;
+    const int64_t num_kb = (K + kBlockK - 1) / kBlockK;
+    int best = kMaxTileX;
+    double best_cost = 1e300;
+    for (int tx = kMaxTileX; tx >= 32; tx -= 16) {
+        const int64_t items = ((M + 2 * tx - 1) / (2 * tx)) * tiles_n;
+        const int64_t rounds = (items + pairs - 1) / pairs;
+        const double cost = (double)rounds * (double)num_kb * (2 * tx + 512);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = tx; }
+    }
+    if (tile_x) *tile_x = best;
+    return best_cost;
+}
 
 bool w8a16_tc_pair_supported(const W8A16Args& a) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
@@ -489,7 +435,7 @@ bool w8a16_tc_pair_supported(const W8A16Args& a) {
     if (a.K < 16 || a.K % 16 != 0) return false;  // TMA: int8 row stride must be a multiple of 16 bytes
     if ((a.ldx * 2) % 16 != 0) return false;      // TMA: activation row stride
     if (!al16(a.x) || !al16(a.wq)) return false;
-    if (a.KO > 64 || a.M < 1 || a.N < 1) return false;
+    if (a.KO > 0 || a.M < 1 || a.N < 1) return false;
     if (sm_count() < 2) return false;
     return encode_fn2() != nullptr;
 }
@@ -500,49 +446,46 @@ cudaError_t launch_w8a16_tc_pair(const W8A16Args& a, cudaStream_t s) {
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.scales = a.scales; p.scales_dtype = a.scales_dtype;
     p.bias = a.bias; p.bias_dtype = a.bias_dtype;
-    p.xo = a.xo; p.wo = a.wo; p.KO = a.KO; p.ldxo = a.ldxo;
     p.y = a.y; p.ldy = a.ldy;
-    p.tile_x = pick_pair_tile_x(a.M, a.N, pairs_avail);
-    p.debug = 0;
-    p.tiles_x = (int)((a.M + p.tile_x - 1) / p.tile_x);
+    w8a16_tc_pair_plan(a.M, a.N, a.K, pairs_avail, &p.tile_x);
+    p.tiles_x = (int)((a.M + 2 * p.tile_x - 1) / (2 * p.tile_x));
     p.tiles_n = (int)((a.N + 255) / 256);
     p.error_flag = w8a16_tc_error_word();
     if (!p.error_flag) return cudaErrorUnknown;
-    p.x_sub_bytes = ((uint32_t)(p.tile_x / 2) * kBlockK * 2 + 1023u) & ~1023u;
-    p.x_stage_bytes = kSub * p.x_sub_bytes;
-    const uint32_t fixed = 1024 + kStagesA * kBytesA + kStagesW8 * kBytesW8 + kTailBytes;
-    int st = (int)((kSmemLimit - fixed) / p.x_stage_bytes);
-    if (st > kMaxStages) st = kMaxStages;
-    if (st < 2) return cudaErrorNotSupported;
-    p.stages = st;
-    const uint32_t smem = fixed + (uint32_t)st * p.x_stage_bytes;
 
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x, map_w, map_pf;
     const CUtensorMapDataType xdt = a.act_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     if (!make_map(&map_x, xdt, a.x, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.ldx * 2, kBlockK, (uint32_t)(p.tile_x / 2),
                   CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorNotSupported;
-    if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kStageK,
-                  kUmmaM, CU_TENSOR_MAP_SWIZZLE_NONE))
+    // the int8 tile is read by the converters' generic loads, one row per lane: 64-byte swizzle
+    if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK, kTileN,
+                  CU_TENSOR_MAP_SWIZZLE_64B))
+        return cudaErrorNotSupported;
+    // the same tensor with a box of kPfBlocks k-blocks, for L2 prefetches only
+    if (!make_map(&map_pf, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K,
+                  a.K >= kPfBlocks * kBlockK ? kPfBlocks * kBlockK : kBlockK, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorNotSupported;
 
-    const int64_t tiles = (int64_t)p.tiles_x * p.tiles_n;
-    const int pairs = (int)(tiles < pairs_avail ? tiles : pairs_avail);
+    const int64_t items = (int64_t)p.tiles_x * p.tiles_n;
+    const int pairs = (int)(items < pairs_avail ? items : pairs_avail);
     const void* fn = a.act_dtype == kBF16 ? (const void*)w8a16_tc_pair_kernel<__nv_bfloat16>
                                           : (const void*)w8a16_tc_pair_kernel<__half>;
     static bool attr_done[64][2] = {};
+    static int max_clusters[64][2] = {};
     int dev = 0;
     cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     const int which = a.act_dtype == kBF16 ? 0 : 1;
-    if (dev >= 0 && dev < 64 && !attr_done[dev][which]) {
-        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+    if (!attr_done[dev][which]) {
+        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_done[dev][which] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -551,24 +494,19 @@ cudaError_t launch_w8a16_tc_pair(const W8A16Args& a, cudaStream_t s) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    {
-        // a persistent schedule needs every pair resident at once: never launch more clusters
-        // than the device can hold simultaneously
-        static int max_clusters[64][2] = {};
-        if (dev >= 0 && dev < 64 && max_clusters[dev][which] == 0) {
-            int n = 0;
-            cudaLaunchConfig_t probe = cfg;
-            probe.gridDim = dim3((unsigned)(2 * pairs_avail));
-            if (cudaOccupancyMaxActiveClusters(&n, fn, &probe) != cudaSuccess || n <= 0) n = pairs_avail;
-            max_clusters[dev][which] = n;
-        }
-        int cap = (dev >= 0 && dev < 64) ? max_clusters[dev][which] : pairs_avail;
-        if (pairs > cap) cfg.gridDim = dim3((unsigned)(2 * cap));
+    if (max_clusters[dev][which] == 0) {
+        // a persistent schedule needs every pair resident at once: never launch more clusters than the device
+        // holds simultaneously
+        int n = 0;
+        cudaLaunchConfig_t probe = cfg;
+        probe.gridDim = dim3((unsigned)(2 * pairs_avail));
+        if (cudaOccupancyMaxActiveClusters(&n, fn, &probe) != cudaSuccess || n <= 0) n = pairs_avail;
+        max_clusters[dev][which] = n;
     }
-    void* args[3] = {(void*)&map_x, (void*)&map_w, (void*)&p};
-    cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
-    if (e != cudaSuccess) return e;
-    return cudaPeekAtLastError();
+    if (pairs > max_clusters[dev][which]) cfg.gridDim = dim3((unsigned)(2 * max_clusters[dev][which]));
+    void* args[4] = {(void*)&map_x, (void*)&map_w, (void*)&map_pf, (void*)&p};
+    const cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+    return e != cudaSuccess ? e : cudaPeekAtLastError();
 }
 
 }  // namespace cb

@@ -381,4 +381,10 @@ def test_two_activation_tiles_per_work_item(M, N, K, KO, bias, dtype):
         ref_order = O.w8a16_forward(x, lay, b)
         ne = int((y.cpu().view(torch.int16) != ref_order.view(torch.int16)).sum())
         assert ne <= 5e-3 * y.numel(), f"{ne} of {y.numel()} values differ from the reference's rounding order"
+        # the CTA-pair kernel (tcgen05.mma.cta_group::2, two activation tiles per item, each CTA loading half of
+        # either): several items per pair, ragged items, the same gates
+        y2 = w8a16_linear(x.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda() if bias else None, path=2)
+        _check(y2, ref, f"pair kernel M={M} N={N} K={K}")
+        ne2 = int((y2.cpu().view(torch.int16) != ref_order.view(torch.int16)).sum())
+        assert ne2 <= 5e-3 * y2.numel(), f"pair kernel: {ne2} of {y2.numel()} values differ from the reference's rounding order"
     assert Nat.device_error_state() == 0

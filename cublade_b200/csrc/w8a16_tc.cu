@@ -81,11 +81,9 @@ constexpr uint32_t kBytesW8 = kTileN * kBlockK;  // 8192
 //           a weight stream whose pace is set by how many k-blocks are in flight, not by the tensor core.
 //   kTmemA64: the same for tiles of at most 64 rows: twelve stages.
 //   kTmemA2: kTmemA with TWO activation tiles of up to 208 rows per work item: a widened weight k-block in tensor
-//           memory is used by two MMAs, one per activation tile, each into its own accumulator.  What bounds the
-//           one-tile modes at large M is shared-memory bandwidth -- per k-block the activation tile is written once
-//           by TMA and read once by the tensor core, the int8 tile written and read once: 112 KiB (kSmemA, 256
-//           rows) or 80 KiB (kTmemA, 208 rows) against 128 B/clk -- and the converters' issue slots; both costs are
-//           per weight k-block, so a second activation tile halves them per output row (120 KiB for 416 rows).
+//           memory is used by two MMAs, one per activation tile, each into its own accumulator: the widening and
+//           the int8 tile's trip through shared memory are per weight k-block, so a second activation tile halves
+//           them per output row (ALU pipe 52 -> 34 %), and the larger items fill the rounds better.
 //           The two accumulators fill tensor memory beside three A stages, so they are not double-buffered: the
 //           next work item's MMAs into an accumulator wait until the epilogue has drained it (a few microseconds
 //           per ~30 us item).
@@ -859,8 +857,9 @@ struct TcPlan {
 constexpr int kMaxSplits = 32;
 // Modelled time of a k-block of the two-tile mode relative to (rows + 512) of the one-tile shared-memory mode.
 // Measured on B200 (N = 14336, K = 4096): a k-block of a 416-row item takes 0.79 us against 0.48 us for a 256-row
-// tile -- the same time per row, both forms are bound by what an SM pulls out of L2 (~80 GB/s per SM: 61 KB and 40 KB
-// per k-block) -- so the two-tile form wins exactly where its larger items fill the rounds better:
+// tile -- the same time per row (a CTA-pair kernel that halves the activation bytes per SM is no faster, nor is a
+// second MMA issuer: the kernel sits at the power cap with the tensor pipe 65 % busy) -- so the two-tile form wins
+// exactly where its larger items fill the rounds better:
 // M = 320 / 416 / 832 / 2048 / 4096 / 8192: 47 / 52 / 97 / 203 / 404 / 917 us against 53 / 56 / 105 / 223 / 428 / 955 us,
 // and loses at M = 256 / 512 / 1024 (45 / 82 / 132 against 41 / 72 / 115 us).
 constexpr double kTwoTileCostFactor = 1.28;

@@ -13,6 +13,8 @@ Beside the headline the line carries
   ``configs``   the other benchmark configurations measured the same way: per-tensor FP8 (4096 x 4096),
                 per-group INT8 (16384 x 8192, groups of 128, bf16 and fp16 dequantize), the W8A16 linear
                 (N = 14336, K = 4096) per M with its end-to-end figure, and its LLM.int8 variant;
+  ``next_rows`` the rows next to the path: fused RMSNorm -> INT8, per-column and non-last-axis per-group INT8 in place,
+                the W8A8 and W4A16 layers, the generic tcgen05 GEMM wrapper (device time only);
   ``sharded``   the multi-GPU forms of the path over the N ranks of this launch (N = 1 is the baseline of
                 the scaling curve): one bf16 tensor of 2^33 elements quantized per tensor to FP8 with its rows
                 split over the ranks (strong scaling; local amax, ONE NCCL max-allreduce of a float32, cast;
@@ -620,6 +622,68 @@ def w8a16_table(rt: Runtime, peaks, ms=(1, 16, 128, 2048), outliers=False):
 
 
 # --------------------------------------------------------------------------------------
+# the rows next to the path (fused RMSNorm -> quantize, other axes, W8A8 / W4A16, the dense GEMM)
+# --------------------------------------------------------------------------------------
+def next_rows(rt: Runtime, peaks, K, warmup):
+    import cublade_b200 as cb
+    from cublade_b200.bindings.triton import matmul
+    from tests.golden import cases
+
+    device = rt.device
+    out = {}
+    wl = RmsnormInt8Workload(device)
+    out["rmsnorm_int8_fused_16384x8192"] = quant_record(
+        wl, measure_quant(rt, wl, min(K, 50), warmup, collective=False, min_s=0.05, e2e=False), peaks, 1)
+    del wl
+    torch.cuda.empty_cache()
+
+    def us(fn, n):
+        g = rt.capture(lambda: [fn(i) for i in range(n)])
+        ms, _ = rt.time_graphs([g], n, min_s=0.03, collective=False)
+        return ms * 1e3
+
+    gen = torch.Generator(device=device).manual_seed(9)
+    xs = [(torch.randn(8192, 8192, generator=gen, device=device) * 0.5).to(torch.bfloat16) for _ in range(3)]
+    n = 8192 * 8192
+    for key, kw in (("int8_per_column_8192x8192_in_place", dict(mode="channel", ch_axis=1)),
+                    ("int8_groups_of_128_down_the_rows_8192x8192_in_place", dict(mode="group", group_size=128, ch_axis=0))):
+        qts = [cb.quantize_tensor(x, dtype=torch.int8, **kw) for x in xs]
+        tq = us(lambda i: cb.quantize_tensor(xs[i % 3], dtype=torch.int8, **kw), 6)
+        td = us(lambda i: cb.dequantize_tensor(qts[(i + 1) % 3]), 6)
+        out[key] = {"quantize_us": tq, "dequantize_us": td, "quantize_gbs_at_3B_per_element": n * 3 / tq / 1e3,
+                    "dequantize_gbs_at_3B_per_element": n * 3 / td / 1e3,
+                    "note": "the reference: NotImplementedError (channel) / two transposing copies around the row kernel (group)"}
+        del qts
+    del xs
+    torch.cuda.empty_cache()
+    w, _, _ = cases.w8a16_weight(False)
+    N_, K_ = cases.W8A16_N, cases.W8A16_K
+    for name, cls, M in (("w8a8_linear_M2048", cb.quantization.cuBladeW8A8LinearLayer, 2048),
+                         ("w4a16_linear_M1", cb.quantization.cuBladeW4A16LinearLayer, 1)):
+        sets = 1 if M >= 1024 else 6
+        layers = []
+        for _ in range(sets):
+            lay = cls(K_, N_, bias=False, dtype=torch.bfloat16)
+            lay.quantize(w.to(device))
+            layers.append(lay.to(device))
+        x = cases.w8a16_activations(M).to(device)
+        for lay in layers:
+            lay(x)
+        t = us(lambda i: layers[i % sets](x), 2 * sets if sets > 1 else 6)
+        out[name] = {"us": t, "tera_ops": 2.0 * M * N_ * K_ / t / 1e6,
+                     "shape": f"M={M} N={N_} K={K_}" + (", per-token activation quantization inside the step" if "w8a8" in name else "")}
+        del layers
+    torch.cuda.empty_cache()
+    a = torch.randn(4096, 4096, generator=gen, device=device).to(torch.bfloat16)
+    b = torch.randn(4096, 4096, generator=gen, device=device).to(torch.bfloat16)
+    matmul(a, b)
+    t = us(lambda i: matmul(a, b), 4)
+    out["matmul_bf16_4096x4096x4096"] = {"us": t, "tflops": 2.0 * 4096 ** 3 / t / 1e6,
+                                         "note": "generic GEMM wrapper on tcgen05 (transpose of B included)"}
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # sharded forms of the path (all ranks take part)
 # --------------------------------------------------------------------------------------
 def _event_ms(pairs):
@@ -1188,6 +1252,7 @@ def main():
                 cfgs["4_w8a16_linear"] = w8a16_table(rt, peaks)
                 cfgs["4p_w8a16_linear_llm_int8"] = w8a16_table(rt, peaks, outliers=True)
                 out["configs"] = cfgs
+                out["next_rows"] = next_rows(rt, peaks, K, warmup)
                 out["w8a16"] = {k: {"us": v["us"], "tflops": v["tflops"], "gbs": v["gbs"], "bound": v["roofline"]["bound"],
                                     "frac": v["roofline"]["frac"]} for k, v in cfgs["4_w8a16_linear"]["per_m"].items()}
                 torch.cuda.empty_cache()

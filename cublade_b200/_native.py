@@ -54,6 +54,8 @@ SIGNATURES = {
     "cb_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int32]),
     "cb_gemm": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_int32, c_void_p,
                           c_size_t, c_void_p]),
+    "cb_matmul": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_int32, c_void_p,
+                            c_size_t, c_void_p]),
     "cb_w4_quantize_rows": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p]),
     "cb_w4_unpack": (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "cb_w4a16_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

@@ -253,6 +253,23 @@ int32_t cb_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, i
                        "cb_gemm", 2);
 }
 
+int32_t cb_matmul(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int32_t in_kind, void* c, int64_t ldc,
+                  int32_t activation, void* workspace, size_t workspace_bytes, void* stream) {
+    if (in_kind < 0 || in_kind > 2) return fail(CB_ERR_DTYPE, "cb_matmul: in_kind must be 0 (fp16), 1 (bf16) or 2 (int8)");
+    if (activation != 0 && activation != 1) return fail(CB_ERR_ARGUMENT, "cb_matmul: activation must be 0 (none) or 1 (leaky_relu)");
+    if (M < 0 || N < 0 || K < 0) return fail(CB_ERR_ARGUMENT, "cb_matmul: negative size");
+    if (M == 0 || N == 0) return CB_OK;
+    if (K == 0) return fail(CB_ERR_ARGUMENT, "cb_matmul: K must be positive");
+    if (!a || !b || !c) return fail(CB_ERR_ARGUMENT, "cb_matmul: null pointer");
+    if (ldc < N) return fail(CB_ERR_ARGUMENT, "cb_matmul: ldc < N");
+    // C has the input type for the float kinds (fp32 accumulation, one rounding), int32 for int8; the activation is
+    // ignored for int8 as in the reference wrapper
+    const int out_kind = in_kind == 0 ? 1 : in_kind == 1 ? 3 : 2;
+    return cuda_result(cb::launch_tc_gemm(a, b, M, N, K, in_kind, c, ldc, out_kind, workspace, workspace_bytes,
+                                          as_stream(stream), in_kind <= 1 ? activation : 0),
+                       "cb_matmul", 2);
+}
+
 int32_t cb_w8a8_linear(const void* xq, const float* x_scales, int64_t M, int64_t K, const void* wq, int64_t N,
                        const void* w_scales, int32_t w_scales_dtype, const void* bias, int32_t bias_dtype, void* y,
                        int64_t ldy, int32_t out_dtype, void* stream) {

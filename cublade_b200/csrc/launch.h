@@ -156,11 +156,12 @@ size_t w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K, bool aligned);
 cudaError_t launch_w4a16(const W4A16Args& a, cudaStream_t s, int* launches);
 
 // ---- dense GEMM C[M, N] = A[M, K] . B[K, N] (fp16 / bf16 -> fp32 accumulate, int8 / uint8 -> int32) ----------
-// in_kind: 0 fp16, 1 bf16, 2 int8, 3 uint8.  out_kind: 0 fp32, 1 fp16 (fp16 inputs only), 2 int32.
+// in_kind: 0 fp16, 1 bf16, 2 int8, 3 uint8.  out_kind: 0 fp32, 1 fp16 (fp16 inputs only), 2 int32, 3 bf16 (bf16 inputs
+// only).  leaky_relu != 0 (float accumulators only): x >= 0 ? x : 0.01 x on the accumulator before it is stored.
 // workspace: tc_gemm_workspace_bytes(N, K, in_kind) bytes for the transposed copy of B.
 size_t tc_gemm_workspace_bytes(int64_t N, int64_t K, int in_kind);
 cudaError_t launch_tc_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int in_kind, void* c,
-                           int64_t ldc, int out_kind, void* workspace, size_t workspace_bytes, cudaStream_t s);
+                           int64_t ldc, int out_kind, void* workspace, size_t workspace_bytes, cudaStream_t s, int leaky_relu = 0);
 
 // reads (and leaves untouched) the per-device flag a kernel raises when one of its bounded waits
 // expired; synchronises the stream.

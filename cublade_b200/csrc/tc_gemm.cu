@@ -49,13 +49,14 @@ struct Smem {
 constexpr uint32_t kSmemBytes = Smem::total + 1024;
 
 enum InKind : int { kInF16 = 0, kInBF16 = 1, kInS8 = 2, kInU8 = 3 };
-enum OutKind : int { kOutF32 = 0, kOutF16 = 1, kOutS32 = 2 };
+enum OutKind : int { kOutF32 = 0, kOutF16 = 1, kOutS32 = 2, kOutBF16 = 3 };
 
 struct Params {
     int64_t M, N, K;
     void* c;
     int64_t ldc;
     int in_kind, out_kind;
+    int leaky_relu;  // 1: float accumulators pass through x >= 0 ? x : 0.01 x before they are stored
     int tile_x, tiles_x, tiles_n;
     int elems_per_stage;  // k elements per stage = 128 / sizeof(element)
     unsigned int* error_flag;
@@ -182,8 +183,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (m >= p.M || ch * 32 + c >= p.tile_x) break;  // uniform across the warp
                     if (!n_ok) continue;
                     // fp32 and int32 accumulators are stored as they are (the same 32 bits)
-                    if (p.out_kind == kOutF16) static_cast<__half*>(p.c)[m * p.ldc + n] = __float2half_rn(__uint_as_float(r[c]));
-                    else static_cast<uint32_t*>(p.c)[m * p.ldc + n] = r[c];
+                    uint32_t bits = r[c];
+                    if (p.leaky_relu) {
+                        const float f = __uint_as_float(bits);
+                        bits = __float_as_uint(f >= 0.0f ? f : 0.01f * f);
+                    }
+                    if (p.out_kind == kOutF16) static_cast<__half*>(p.c)[m * p.ldc + n] = __float2half_rn(__uint_as_float(bits));
+                    else if (p.out_kind == kOutBF16) static_cast<__nv_bfloat16*>(p.c)[m * p.ldc + n] = __float2bfloat16_rn(__uint_as_float(bits));
+                    else static_cast<uint32_t*>(p.c)[m * p.ldc + n] = bits;
                 }
             };
             uint32_t ra[32], rb[32];
@@ -251,13 +258,15 @@ template <> __device__ __forceinline__ int widen_in<uint8_t, int>(uint8_t v) { r
 template <typename E, typename Acc>
 __global__ void __launch_bounds__(256) gemm_simple_kernel(const E* __restrict__ a, const E* __restrict__ b, int64_t M,
                                                           int64_t N, int64_t K, void* __restrict__ c, int64_t ldc,
-                                                          int out_kind) {
+                                                          int out_kind, int leaky_relu) {
     const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (idx >= M * N) return;
     const int64_t m = idx / N, n = idx - m * N;
     Acc acc = 0;
     for (int64_t k = 0; k < K; ++k) acc += widen_in<E, Acc>(a[m * K + k]) * widen_in<E, Acc>(b[k * N + n]);
+    if (leaky_relu && acc < (Acc)0) acc = (Acc)(0.01f * (float)acc);  // float accumulators only (the entry point checks)
     if (out_kind == kOutF16) static_cast<__half*>(c)[m * ldc + n] = __float2half_rn((float)acc);
+    else if (out_kind == kOutBF16) static_cast<__nv_bfloat16*>(c)[m * ldc + n] = __float2bfloat16_rn((float)acc);
     else static_cast<Acc*>(c)[m * ldc + n] = acc;
 }
 
@@ -311,7 +320,7 @@ size_t tc_gemm_workspace_bytes(int64_t N, int64_t K, int in_kind) {
 }
 
 cudaError_t launch_tc_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int in_kind, void* c,
-                           int64_t ldc, int out_kind, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+                           int64_t ldc, int out_kind, void* workspace, size_t workspace_bytes, cudaStream_t s, int leaky_relu) {
     const int elem = in_kind <= kInBF16 ? 2 : 1;
     auto al16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
     const bool tc_ok = (K * elem) % 16 == 0 && K * elem >= 16 && al16(a) && workspace && al16(workspace) &&
@@ -319,10 +328,10 @@ cudaError_t launch_tc_gemm(const void* a, const void* b, int64_t M, int64_t N, i
     if (!tc_ok) {
         const unsigned grid = (unsigned)((M * N + 255) / 256);
         switch (in_kind) {
-            case kInF16: gemm_simple_kernel<__half, float><<<grid, 256, 0, s>>>(static_cast<const __half*>(a), static_cast<const __half*>(b), M, N, K, c, ldc, out_kind); break;
-            case kInBF16: gemm_simple_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), M, N, K, c, ldc, out_kind); break;
-            case kInS8: gemm_simple_kernel<int8_t, int><<<grid, 256, 0, s>>>(static_cast<const int8_t*>(a), static_cast<const int8_t*>(b), M, N, K, c, ldc, out_kind); break;
-            default: gemm_simple_kernel<uint8_t, int><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), M, N, K, c, ldc, out_kind); break;
+            case kInF16: gemm_simple_kernel<__half, float><<<grid, 256, 0, s>>>(static_cast<const __half*>(a), static_cast<const __half*>(b), M, N, K, c, ldc, out_kind, leaky_relu); break;
+            case kInBF16: gemm_simple_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), M, N, K, c, ldc, out_kind, leaky_relu); break;
+            case kInS8: gemm_simple_kernel<int8_t, int><<<grid, 256, 0, s>>>(static_cast<const int8_t*>(a), static_cast<const int8_t*>(b), M, N, K, c, ldc, out_kind, leaky_relu); break;
+            default: gemm_simple_kernel<uint8_t, int><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), M, N, K, c, ldc, out_kind, leaky_relu); break;
         }
         return cudaPeekAtLastError();
     }
@@ -335,7 +344,7 @@ cudaError_t launch_tc_gemm(const void* a, const void* b, int64_t M, int64_t N, i
     // 2. the GEMM
     const int sms = sm_count();
     Params p;
-    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.in_kind = in_kind; p.out_kind = out_kind;
+    p.M = M; p.N = N; p.K = K; p.c = c; p.ldc = ldc; p.in_kind = in_kind; p.out_kind = out_kind; p.leaky_relu = leaky_relu;
     p.tile_x = pick_tile_x(M, N, sms);
     p.tiles_x = (int)((M + p.tile_x - 1) / p.tile_x);
     p.tiles_n = (int)((N + kTileN - 1) / kTileN);

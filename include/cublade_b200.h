@@ -172,6 +172,16 @@ size_t cb_gemm_workspace_bytes(int64_t N, int64_t K, int32_t in_kind);
 int32_t cb_gemm(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int32_t in_kind, void* c, int64_t ldc,
                 int32_t out_kind, void* workspace, size_t workspace_bytes, void* stream);
 
+/* C[M, N] = activation(A[M, K] . B[K, N]) with C in the INPUT type, the contract of the reference's generic wrapper
+ *   matmul(A, B, activation="", override_config=None, use_autotune=True)  cublade/bindings/triton/matmul.py:17-132
+ *   (kernel cublade/kernels/triton/matmul_kernel.py:9-105: accumulate, optional leaky_relu on the accumulator,
+ *   one cast to the output type)
+ * in_kind 0 fp16 -> fp16, 1 bf16 -> bf16 (fp32 accumulation), 2 int8 -> int32 (activation ignored, as there).
+ * activation: 0 none, 1 leaky_relu (x >= 0 ? x : 0.01 x).  The reference's tuning arguments have no meaning here.
+ * Its float32 and float8_e5m2 inputs are not served (CB_ERR_DTYPE).  workspace as for cb_gemm. */
+int32_t cb_matmul(const void* a, const void* b, int64_t M, int64_t N, int64_t K, int32_t in_kind, void* c, int64_t ldc,
+                  int32_t activation, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------
  * W4A16 linear: 4-bit symmetric weights (codes in [-7, 7], one scale per output feature), 16-bit activations,
  * fp32 accumulation:   y[m, n] = T( (sum_k x[m, k] * code[n, k]) * scales[n] + bias[n] )

@@ -61,3 +61,32 @@ def test_argument_checks_follow_the_reference():
     with pytest.raises(RuntimeError, match="int32"):
         wmma_gemm(a.to(torch.int8), a.to(torch.int8), torch.float32)
     assert N.device_error_state() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 96, 128), (300, 520, 1000), (2048, 1024, 4096), (5, 7, 9)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.int8])
+@pytest.mark.parametrize("activation", ["", "leaky_relu"])
+def test_generic_matmul_wrapper(M, N, K, dtype, activation):
+    """matmul(A, B, activation) with the contract of cublade/bindings/triton/matmul.py:17-132: C in the input dtype
+    (int32 for int8), leaky_relu applied to the fp32 accumulator before the one rounding, ignored for int8."""
+    from cublade_b200.bindings.triton import matmul
+
+    g = torch.Generator().manual_seed(M + N + K)
+    if dtype == torch.int8:
+        a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+        b = torch.randint(-128, 128, (K, N), generator=g, dtype=torch.int8)
+        want = (a.double() @ b.double()).to(torch.int32)
+        got = matmul(a.cuda(), b.cuda(), activation=activation).cpu()
+        assert got.dtype == torch.int32 and torch.equal(got, want)
+        return
+    a = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(K, N, generator=g).to(dtype)
+    ref = a.double() @ b.double()
+    if activation == "leaky_relu":
+        ref = torch.where(ref >= 0, ref, 0.01 * ref)
+    got = matmul(a.cuda(), b.cuda(), activation=activation, override_config={"BLOCK_M": 64}, use_autotune=False).cpu()
+    assert got.dtype == dtype and got.shape == (M, N)
+    err = (got.double() - ref).norm() / ref.norm()
+    assert err < (3e-3 if dtype == torch.bfloat16 else 5e-4), err  # one rounding to the 16-bit type
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        matmul(a.float().cuda(), b.float().cuda())

@@ -686,10 +686,6 @@ def next_rows(rt: Runtime, peaks, K, warmup):
 # --------------------------------------------------------------------------------------
 # sharded forms of the path (all ranks take part)
 # --------------------------------------------------------------------------------------
-def _event_ms(pairs):
-    return [a.elapsed_time(b) for a, b in pairs]
-
-
 def sharded_fp8(rt: Runtime, checks, total=1 << 33, chunk=1 << 27, steps=5):
     """ONE bf16 tensor of `total` elements, N(0, 1), chunk c generated on its owning device from a seed that depends
     only on c (the content does not depend on the number of GPUs), rows split contiguously over the ranks.  A step is

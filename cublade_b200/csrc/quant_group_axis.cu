@@ -67,16 +67,19 @@ struct LaneAbsMax<__nv_bfloat16> : LaneAbsMax16<__nv_bfloat16, __nv_bfloat162> {
 // x viewed as packs: [outer, C, ppr] packs, ppr = inner / E.  One work item = (o, group cg, pack ip); a CTA of
 // kWarps warps takes 32 consecutive items -- lane = item, so a warp's loads of one row are 32 adjacent packs -- and
 // warp w takes rows w, w + kWarps, ... of the groups (four loads in flight per thread).  The per-lane maxima of the
-// warps meet in shared memory; every thread then derives its items' reciprocals and encodes its own rows again
-// (second read served by L2).
+// warps meet in shared memory; every thread then derives its items' reciprocals and encodes its own rows -- kept in
+// registers for groups of up to 128 rows, read a second time (from L2) for longer ones.
 constexpr int kWarps = kBlock / 32;
 
-template <typename T>
+// R > 0: the thread's rows (at most R = ceil(G / kWarps) of them) stay in registers between the maximum and the encode,
+// so x is read once; R == 0: any G, the rows are read a second time (from L2).
+template <typename T, int R>
 __global__ void __launch_bounds__(kBlock) quant_group_axis_kernel(const T* __restrict__ x, int64_t items, int64_t C,
                                                                   int64_t ppr, int G, float eps,
                                                                   uint8_t* __restrict__ q,
                                                                   float* __restrict__ scale_out) {
     constexpr int E = DTypeTraits<T>::kLanes;
+    constexpr int RR = R > 0 ? R : 1;
     pdl_trigger();
     __shared__ float red[kWarps][E][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -87,16 +90,27 @@ __global__ void __launch_bounds__(kBlock) quant_group_axis_kernel(const T* __res
     const int64_t ip = live ? w % ppr : 0, og = live ? w / ppr : 0, cg = og % ngr, o = og / ngr;
     const int64_t pack0 = (o * C + cg * G) * ppr + ip;  // pack of row j of the group: pack0 + j * ppr
     LaneAbsMax<T> am;
+    uint4 held[RR];
     if (live) {
-        int j = warp;
-        for (; j + 3 * kWarps < G; j += 4 * kWarps) {
-            const uint4 v0 = ld_keep16(xp + pack0 + (int64_t)(j + 0 * kWarps) * ppr);
-            const uint4 v1 = ld_keep16(xp + pack0 + (int64_t)(j + 1 * kWarps) * ppr);
-            const uint4 v2 = ld_keep16(xp + pack0 + (int64_t)(j + 2 * kWarps) * ppr);
-            const uint4 v3 = ld_keep16(xp + pack0 + (int64_t)(j + 3 * kWarps) * ppr);
-            am.update(v0); am.update(v1); am.update(v2); am.update(v3);
+        if constexpr (R > 0) {
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const int j = warp + k * kWarps;
+                held[k] = j < G ? ld_stream16(xp + pack0 + (int64_t)j * ppr) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int k = 0; k < R; ++k) am.update(held[k]);
+        } else {
+            int j = warp;
+            for (; j + 3 * kWarps < G; j += 4 * kWarps) {
+                const uint4 v0 = ld_keep16(xp + pack0 + (int64_t)(j + 0 * kWarps) * ppr);
+                const uint4 v1 = ld_keep16(xp + pack0 + (int64_t)(j + 1 * kWarps) * ppr);
+                const uint4 v2 = ld_keep16(xp + pack0 + (int64_t)(j + 2 * kWarps) * ppr);
+                const uint4 v3 = ld_keep16(xp + pack0 + (int64_t)(j + 3 * kWarps) * ppr);
+                am.update(v0); am.update(v1); am.update(v2); am.update(v3);
+            }
+            for (; j < G; j += kWarps) am.update(ld_keep16(xp + pack0 + (int64_t)j * ppr));
         }
-        for (; j < G; j += kWarps) am.update(ld_keep16(xp + pack0 + (int64_t)j * ppr));
     }
     float amax[E], inv[E];
     am.finish(amax);
@@ -114,15 +128,26 @@ __global__ void __launch_bounds__(kBlock) quant_group_axis_kernel(const T* __res
         if (live && warp == (l % kWarps)) scale_out[(o * inner + ip * E + l) * ngr + cg] = is.scale;
     }
     if (!live) return;
-    for (int j = warp; j < G; j += kWarps) {
-        const int64_t p = pack0 + (int64_t)j * ppr;
+    auto encode_store = [&](const uint4& raw, int64_t p) {
         float f[E];
-        pack_to_floats<T>(ld_stream16(xp + p), f);
+        pack_to_floats<T>(raw, f);
 #pragma unroll
         for (int l = 0; l < E; ++l) f[l] = __fmul_rn(f[l], inv[l]);
         const uint32_t lo = Int8Code::encode4(f[0], f[1], f[2], f[3]);
         if constexpr (E == 8) st_stream8(q + p * 8, make_uint2(lo, Int8Code::encode4(f[4], f[5], f[6], f[7])));
         else st_stream4(q + p * 4, lo);
+    };
+    if constexpr (R > 0) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const int j = warp + k * kWarps;
+            if (j < G) encode_store(held[k], pack0 + (int64_t)j * ppr);
+        }
+    } else {
+        for (int j = warp; j < G; j += kWarps) {
+            const int64_t p = pack0 + (int64_t)j * ppr;
+            encode_store(ld_stream16(xp + p), p);
+        }
     }
 }
 
@@ -233,7 +258,10 @@ cudaError_t quant_t(const void* xv, int64_t outer, int64_t C, int64_t inner, int
         const int64_t ppr = inner / E, items = outer * (C / G) * ppr;
         const int64_t ctas = (items + 31) / 32;
         if (ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
-        quant_group_axis_kernel<T><<<(unsigned)ctas, kBlock, 0, s>>>(x, items, C, ppr, G, eps, q, scale_out);
+        const int rows_per_thread = (G + kWarps - 1) / kWarps;
+        if (rows_per_thread <= 4) quant_group_axis_kernel<T, 4><<<(unsigned)ctas, kBlock, 0, s>>>(x, items, C, ppr, G, eps, q, scale_out);
+        else if (rows_per_thread <= 16) quant_group_axis_kernel<T, 16><<<(unsigned)ctas, kBlock, 0, s>>>(x, items, C, ppr, G, eps, q, scale_out);
+        else quant_group_axis_kernel<T, 0><<<(unsigned)ctas, kBlock, 0, s>>>(x, items, C, ppr, G, eps, q, scale_out);
     } else {
         const int64_t items = outer * (C / G) * inner;
         quant_group_axis_scalar_kernel<T><<<grid_for(items, 8), kBlock, 0, s>>>(x, items, C, inner, G, eps, q, scale_out);

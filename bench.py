@@ -385,7 +385,7 @@ class Runtime:
         e1.record()
         torch.cuda.synchronize()
         once = max(e0.elapsed_time(e1) * 1e-3, 1e-6)
-        reps = max(1, math.ceil(min_s / once))
+        reps = max(1, math.ceil(1.1 * min_s / once))  # the probe replay can be slower than the steady state
         if collective:
             reps = int(self.max_over_ranks(float(reps)))
             self.barrier()

@@ -60,6 +60,7 @@ NCU_TRAFFIC_BYTES = {
     "int8_channel": {"quantize": 164_258_409, "dequantize": 140_661_321},
     "fp8_tensor": {"quantize": 67_135_317, "dequantize": 16_789_163},
     "int8_group": {"quantize": 362_416_971, "dequantize": 346_577_701},
+    "int8_group_axis0": {"quantize": 167_694_528, "dequantize": 143_982_496},
 }
 
 
@@ -293,6 +294,37 @@ class Int8GroupWorkload(Int8ChannelWorkload):
         return O.int8_dequantize_rows(q, s, torch.bfloat16)
 
 
+class Int8GroupAxis0Workload(Int8GroupWorkload):
+    """INT8 per-group quantize + dequantize with the groups of 128 running DOWN the rows of a bf16 [rows, cols]
+    matrix (ch_axis = 0), in place: the reference makes two transposing copies around its row kernel for this."""
+
+    name = "int8_group_axis0"
+    dominant = "quant_group_axis_kernel (one-pass per-group INT8 quantize, groups along a non-last axis)"
+
+    def __init__(self, device, rows=8192, cols=8192, sets=3, group=128):
+        super().__init__(device, rows, cols, sets, group)
+
+    def config(self):
+        return {"workload": (f"int8_per_group_{self.group}_along_axis0_quant+dequant bf16 {self.rows}x{self.cols} "
+                             f"(Student-t nu=3 x0.5)"),
+                "bytes_per_step": self.bytes_per_step, "seed": 2}
+
+    def quantize(self, x):
+        import cublade_b200 as cb
+
+        return cb.quantize_tensor(x, dtype=torch.int8, mode="group", group_size=self.group, ch_axis=0)
+
+    def extra_kernels(self):
+        return {}
+
+    def cpu_step(self, x_cpu):
+        from oracle import oracle as O
+
+        xt = x_cpu.t().contiguous()
+        q, s = O.int8_quantize_group(xt.view(-1, self.group), self.group)
+        return O.int8_dequantize_rows(q, s, torch.bfloat16).view(self.cols, self.rows).t().contiguous()
+
+
 class RmsnormInt8Workload(Int8ChannelWorkload):
     """Fused RMSNorm -> per-token INT8 quantize of bf16 activations [tokens, hidden], then dequantize."""
 
@@ -334,7 +366,7 @@ class RmsnormInt8Workload(Int8ChannelWorkload):
 
 
 WORKLOADS = {"int8_channel": Int8ChannelWorkload, "fp8_tensor": Fp8TensorWorkload, "int8_group": Int8GroupWorkload,
-             "rmsnorm_int8": RmsnormInt8Workload}
+             "int8_group_axis0": Int8GroupAxis0Workload, "rmsnorm_int8": RmsnormInt8Workload}
 LINEAR_WORKLOADS = ("w8a16", "w8a8", "w4a16")
 
 

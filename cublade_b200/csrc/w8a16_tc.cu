@@ -415,15 +415,6 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const bool has_next = work_item(p, num_kb, idx + 1, nx);
                 const int row_w_next = has_next ? (nx.tile / p.tiles_x) * kTileN : 0;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    {
-                        // the int8 staging buffer of a stage is free when the stage is: the MMAs that retired
-                        // consumed what the converters made of it
-                        ok = mbar_wait(empty_a + 8 * s, ph ^ 1u, abort_flag);
-                    }
-                    if (!ok) break;
-                    mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
-                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, row_w, full_w8 + 8 * s);
-                    // (After the load, not before it: the first tile of a launch otherwise lands 0.8 us later.)
                     // One prefetch covers kPfBlocks k-blocks (a wider box of the same tensor): every instruction
                     // of this thread costs 100-250 cycles of issue, and with a prefetch per k-block its loop
                     // (~600 cycles) paced the whole kernel for short activation tiles.
@@ -432,6 +423,14 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         else if (has_next && nx.kb0 + (kb + kAhead - w.kb1) < nx.kb1)
                             tma_prefetch_l2_2d(&map_pf, (nx.kb0 + kb + kAhead - w.kb1) * kBlockK, row_w_next);
                     }
+                    {
+                        // the int8 staging buffer of a stage is free when the stage is: the MMAs that retired
+                        // consumed what the converters made of it
+                        ok = mbar_wait(empty_a + 8 * s, ph ^ 1u, abort_flag);
+                    }
+                    if (!ok) break;
+                    mbar_expect_tx(full_w8 + 8 * s, kBytesW8);
+                    tma_load_2d(sw8 + s * kBytesW8, &map_w, kb * kBlockK, row_w, full_w8 + 8 * s);
                     if (++s == kStagesW8) { s = 0; ph ^= 1u; }
                 }
             }

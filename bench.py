@@ -1198,6 +1198,46 @@ def cpu_baseline(wl, budget_s=12.0):
                       "(PyTorch CPU formulation of the reference ops)"}
 
 
+def single_gpu_extras(rt: Runtime, peaks, K, warmup):
+    """The other configurations and the rows next to the path, one GPU: `configs`, `next_rows`, `w8a16`."""
+    device = rt.device
+    cfgs = {}
+    for key, cls in (("1_fp8_per_tensor_4096x4096", Fp8TensorWorkload),
+                     ("3_int8_per_group128_16384x8192", Int8GroupWorkload)):
+        w2 = cls(device)
+        r2 = measure_quant(rt, w2, min(K, 100), warmup, collective=False, min_s=0.1)
+        cfgs[key] = quant_record(w2, r2, peaks, 1)
+        del w2, r2
+        torch.cuda.empty_cache()
+    cfgs["4_w8a16_linear"] = w8a16_table(rt, peaks)
+    cfgs["4p_w8a16_linear_llm_int8"] = w8a16_table(rt, peaks, outliers=True)
+    return {"configs": cfgs, "next_rows": next_rows(rt, peaks, K, warmup),
+            "w8a16": {k: {"us": v["us"], "tflops": v["tflops"], "gbs": v["gbs"], "bound": v["roofline"]["bound"],
+                          "frac": v["roofline"]["frac"]} for k, v in cfgs["4_w8a16_linear"]["per_m"].items()}}
+
+
+def single_gpu_extras_in_child(K, warmup, local_rank):
+    """Runs single_gpu_extras() in a process of its own on the same GPU and returns its three keys.  These are some
+    hundred thousand launches of a dozen kernels beside the headline measurement; a CUDA error in any of them is
+    sticky for the process that met it, and it must not cost the line the headline (already measured by the caller) and
+    the sharded forms.  A child that fails is reported under the same keys."""
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "MASTER_ADDR", "MASTER_PORT")
+           and not k.startswith("TORCHELASTIC")}
+    env["LOCAL_RANK"] = str(local_rank)
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--section", "single_gpu_extras", "--steps", str(K),
+           "--warmup", str(warmup)]
+    try:
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1200)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        if r.returncode == 0 and lines:
+            return json.loads(lines[-1])
+        why = f"exit status {r.returncode}: {r.stderr.strip().splitlines()[-1][:300] if r.stderr.strip() else 'no output'}"
+    except subprocess.TimeoutExpired:
+        why = "no result within 1200 s"
+    return {k: {"error": why} for k in ("configs", "next_rows", "w8a16")}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1213,6 +1253,7 @@ def main():
     ap.add_argument("--selftest", action="store_true", help="exit with status 1 when a sharded-form check fails")
     ap.add_argument("--sharded-elements-log2", type=int, default=33,
                     help="size of the sharded per-tensor FP8 tensor (default 2^33 elements; tests use less)")
+    ap.add_argument("--section", default="", help=argparse.SUPPRESS)  # internal: see single_gpu_extras_in_child
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -1242,6 +1283,9 @@ def main():
         if args.workload in LINEAR_WORKLOADS:
             run_linear(args, rt)
             return 0
+        if args.section == "single_gpu_extras":
+            print(json.dumps(single_gpu_extras(rt, _peaks(), args.steps, max(args.warmup, 3))))
+            return 0
         warmup = max(args.warmup, 3)
         K = args.steps
         peaks = _peaks()
@@ -1269,21 +1313,7 @@ def main():
         if not args.no_extras:
             # ---- the other configurations, one GPU each: rank 0 measures, the others wait at the barrier ----
             if rank == 0:
-                cfgs = {}
-                for key, cls in (("1_fp8_per_tensor_4096x4096", Fp8TensorWorkload),
-                                 ("3_int8_per_group128_16384x8192", Int8GroupWorkload)):
-                    w2 = cls(device)
-                    r2 = measure_quant(rt, w2, min(K, 100), warmup, collective=False, min_s=0.1)
-                    cfgs[key] = quant_record(w2, r2, peaks, 1)
-                    del w2, r2
-                    torch.cuda.empty_cache()
-                cfgs["4_w8a16_linear"] = w8a16_table(rt, peaks)
-                cfgs["4p_w8a16_linear_llm_int8"] = w8a16_table(rt, peaks, outliers=True)
-                out["configs"] = cfgs
-                out["next_rows"] = next_rows(rt, peaks, K, warmup)
-                out["w8a16"] = {k: {"us": v["us"], "tflops": v["tflops"], "gbs": v["gbs"], "bound": v["roofline"]["bound"],
-                                    "frac": v["roofline"]["frac"]} for k, v in cfgs["4_w8a16_linear"]["per_m"].items()}
-                torch.cuda.empty_cache()
+                out.update(single_gpu_extras_in_child(K, warmup, local_rank))
             rt.barrier()
             # ---- the sharded forms, all ranks ----
             sh = {"fp8_per_tensor_2p%d" % args.sharded_elements_log2:

@@ -43,3 +43,13 @@ def test_group_axis0_cpu_arm_matches_the_oracle(bench):
     x = wl.cpu_input()
     q = O.quantize_tensor(x, dtype=torch.int8, mode="group", group_size=128, ch_axis=0)
     assert torch.equal(wl.cpu_step(x), O.dequantize_tensor(q))
+
+
+def test_failed_child_is_reported_under_its_keys(bench):
+    """Without a GPU the child process of the secondary measurements exits with an error: the caller gets the three
+    keys with the reason instead of an exception (its own measurements survive a failure of that process)."""
+    if torch.cuda.is_available():
+        pytest.skip("the child would run the measurements here")
+    got = bench.single_gpu_extras_in_child(2, 3, 0)
+    assert set(got) == {"configs", "next_rows", "w8a16"}
+    assert all("error" in v and "exit status" in v["error"] for v in got.values())

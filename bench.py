@@ -721,7 +721,7 @@ def next_rows(rt: Runtime, peaks, K, warmup):
 def sharded_fp8(rt: Runtime, checks, total=1 << 33, chunk=1 << 27, steps=5):
     """ONE bf16 tensor of `total` elements, N(0, 1), chunk c generated on its owning device from a seed that depends
     only on c (the content does not depend on the number of GPUs), rows split contiguously over the ranks.  A step is
-    local amax -> ONE NCCL all_reduce(MAX) of a float32 -> cast of the local shard -> dequantize of the local shard;
+    local amax -> ONE exchange of a float32 maximum -> cast of the local shard -> dequantize of the local shard;
     every phase is timed with CUDA events on the launching stream, the step is the max over ranks."""
     import cublade_b200 as cb
     from cublade_b200 import workloads as W
@@ -739,12 +739,14 @@ def sharded_fp8(rt: Runtime, checks, total=1 << 33, chunk=1 << 27, steps=5):
     x = x.view(-1, 8192)
     zp = torch.zeros((), dtype=torch.float32, device=device)
 
-    def phases(record):
+    def phases(record, exchange):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         ev[0].record()
         amax = amax_abs(x)
         ev[1].record()
-        if dist is not None:
+        if exchange is not None:
+            amax = exchange.exchange(amax)
+        elif dist is not None:
             dist.all_reduce(amax, op=dist.ReduceOp.MAX)
         ev[2].record()
         q, scale = cast_per_tensor(x, amax, torch.float8_e4m3fn, 1e-12)
@@ -755,21 +757,47 @@ def sharded_fp8(rt: Runtime, checks, total=1 << 33, chunk=1 << 27, steps=5):
             record.append(ev)
         return amax, q, scale, y
 
-    for _ in range(2):
-        out = phases(None)
-    del out
-    rt.barrier()
-    rec = []
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        amax, q, scale, y = phases(rec)
-    e1.record()
-    rt.barrier()
-    step_ms = rt.max_over_ranks(e0.elapsed_time(e1) / steps)
-    names = ("amax", "allreduce", "cast", "dequantize")
-    mine = [statistics.median(ev[i].elapsed_time(ev[i + 1]) for ev in rec) for i in range(4)]
-    worst = rt.max_over_ranks(*mine)
+    def timed(exchange):
+        for _ in range(2):
+            out = phases(None, exchange)
+        del out
+        rt.barrier()
+        rec = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            res = phases(rec, exchange)
+        e1.record()
+        rt.barrier()
+        ms = rt.max_over_ranks(e0.elapsed_time(e1) / steps)
+        mine = [statistics.median(ev[i].elapsed_time(ev[i + 1]) for ev in rec) for i in range(4)]
+        return ms, rt.max_over_ranks(*mine), res
+
+    # The exchange between the phases: NCCL's all_reduce(MAX) of one float, and -- where torch's symmetric memory maps
+    # the ranks' buffers into one another -- the library's own peer-memory exchange (a 64-bit store per peer over
+    # NVLink and a bounded wait, one small kernel per rank).  Both are timed; every rank must agree on which ran.
+    peer, peer_why = None, "one rank"
+    if dist is not None:
+        from cublade_b200.sharding import PeerAmaxExchange
+
+        try:
+            peer = PeerAmaxExchange()
+            built = 1.0
+        except Exception as e:  # no symmetric memory on this system: the collective stays
+            peer, built, peer_why = None, 0.0, f"{type(e).__name__}: {str(e)[:160]}"
+        if -rt.max_over_ranks(-built) < 1.0:
+            peer = None
+    names = ("amax", "exchange", "cast", "dequantize")
+    nccl_ms = nccl_worst = None
+    if peer is not None:
+        nccl_ms, nccl_worst, res = timed(None)
+        nccl_scale_bits = int(res[2].view(torch.int32).item())
+        del res
+        torch.cuda.empty_cache()
+    step_ms, worst, (amax, q, scale, y) = timed(peer)
+    if peer is not None:
+        checks.append(("fp8_sharded: the peer-memory exchange gives the scale the NCCL all-reduce gives",
+                       bool(nccl_scale_bits == int(scale.view(torch.int32).item()))))
     # ---- checks: the same scale everywhere; checksums that do not depend on the number of ranks ----
     local_amax = amax_abs(x)
     sums = torch.stack([q.view(torch.uint8).sum(dtype=torch.int64),
@@ -804,11 +832,16 @@ def sharded_fp8(rt: Runtime, checks, total=1 << 33, chunk=1 << 27, steps=5):
     total_bytes = total * 8  # quantize 5 B/elem (two compulsory passes over x: the shard cannot stay on chip) + dequantize 3
     rec_out = {
         "workload": f"fp8_e4m3_per_tensor_sharded_quant+dequant bf16 2^{total.bit_length() - 1} elements N(0,1) over "
-                    f"{rt.world} GPU(s), one NCCL max-allreduce of the fp32 amax per step",
+                    f"{rt.world} GPU(s), one max-exchange of the fp32 amax per step",
         "scaling": "strong", "elements": total, "elements_per_rank": n_local, "steps": steps,
         "ms_per_step": step_ms, "value": total_bytes / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
         "per_gpu_gbs": total_bytes / (step_ms * 1e-3) / 1e9 / rt.world,
+        "exchange": ("peer memory: cb_amax_peer_exchange, one 64-bit store per peer over NVLink + a bounded wait"
+                     if peer is not None else "none (one rank)" if dist is None
+                     else f"NCCL all_reduce(MAX) of one float32 (peer-memory form not used: {peer_why})"),
         "phase_ms_max_over_ranks": dict(zip(names, worst)),
+        "with_nccl_all_reduce": (None if nccl_ms is None else
+                                 {"ms_per_step": nccl_ms, "phase_ms_max_over_ranks": dict(zip(names, nccl_worst))}),
         "phase_gbs_per_gpu": {"amax": n_local * 2 / (worst[0] * 1e-3) / 1e9, "cast": n_local * 3 / (worst[2] * 1e-3) / 1e9,
                               "dequantize": n_local * 3 / (worst[3] * 1e-3) / 1e9},
         "amax": a, "scale_bits": int(scale_bits.item()),

@@ -41,6 +41,9 @@ SIGNATURES = {
     "cb_dequantize_per_group_int8": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p]),
     "cb_amax_abs": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p]),
     "cb_cast_per_tensor": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_float, c_int32, c_void_p, c_void_p, c_void_p]),
+    "cb_peer_exchange_state_bytes": (c_int32, []),
+    "cb_peer_exchange_max_ranks": (c_int32, []),
+    "cb_amax_peer_exchange": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
     "cb_w8a16_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "cb_w8a16_linear": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int32, c_void_p,
                                    c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p,

@@ -2,7 +2,8 @@
 
 ``amax_abs`` is the first kernel of the reference's per-tensor quantizers and ``cast_per_tensor`` the
 second (cublade/kernels/cuda/quantization/quantize_per_tensor_fp8.cu:140-159,
-quantize_int8.cu:394-410); between them a caller max-reduces the fp32 amax across ranks.
+quantize_int8.cu:394-410); between them a caller max-reduces the fp32 amax across ranks -- with a collective of its
+own, or with ``amax_peer_exchange`` (peer-memory stores over NVLink, one small kernel per rank).
 """
 from __future__ import annotations
 
@@ -37,3 +38,25 @@ def cast_per_tensor(x: torch.Tensor, amax: torch.Tensor, dtype: torch.dtype, eps
         N.check(N.lib().cb_cast_per_tensor(x.data_ptr(), N.dtype_code(x.dtype), x.numel(), amax.data_ptr(), float(eps),
                                            _CODE[dtype], q.data_ptr(), scale.data_ptr(), N.stream_ptr(x)))
     return q, scale
+
+
+def amax_peer_exchange(local_amax: torch.Tensor, peer_state_ptrs, rank: int) -> torch.Tensor:
+    """Maximum of the ranks' ``local_amax`` through peer memory: ``peer_state_ptrs[r]`` is the address, in THIS process,
+    of rank ``r``'s state array (``peer_exchange_state_bytes()`` bytes, zeroed once before the first exchange).  Every
+    rank must call it once per exchange; the kernels wait for one another with a bounded wait (NaN and the device
+    error flag when a peer does not arrive)."""
+    import ctypes
+
+    if local_amax.dtype != torch.float32 or local_amax.numel() != 1 or not local_amax.is_cuda:
+        raise ValueError("amax_peer_exchange: local_amax must be a 1-element float32 CUDA tensor")
+    world = len(peer_state_ptrs)
+    ptrs = (ctypes.c_void_p * world)(*[int(p) for p in peer_state_ptrs])
+    with N.device_guard(local_amax):
+        out = torch.empty(1, dtype=torch.float32, device=local_amax.device)
+        N.check(N.lib().cb_amax_peer_exchange(local_amax.data_ptr(), ptrs, int(rank), world, out.data_ptr(),
+                                              N.stream_ptr(local_amax)))
+    return out
+
+
+def peer_exchange_state_bytes() -> int:
+    return int(N.lib().cb_peer_exchange_state_bytes())

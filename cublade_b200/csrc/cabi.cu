@@ -89,6 +89,20 @@ int32_t cb_amax_abs(const void* x, int32_t dtype, int64_t n, float* amax, void* 
     return cuda_result(cb::launch_amax_tensor(x, dtype, n, amax, as_stream(stream)), "cb_amax_abs", n > 0 ? 1 : 0);
 }
 
+int32_t cb_peer_exchange_state_bytes(void) { return cb::peer_exchange_state_words() * 8; }
+int32_t cb_peer_exchange_max_ranks(void) { return cb::peer_exchange_max_ranks(); }
+
+int32_t cb_amax_peer_exchange(const float* local_amax, const void* const* peer_state, int32_t rank, int32_t world,
+                              float* out_amax, void* stream) {
+    const char* name = "cb_amax_peer_exchange";
+    if (!local_amax || !peer_state || !out_amax) return fail(CB_ERR_ARGUMENT, "%s: null pointer", name);
+    if (world < 1 || world > cb::peer_exchange_max_ranks() || rank < 0 || rank >= world)
+        return fail(CB_ERR_RANGE, "%s: rank %d / world %d outside 1..%d", name, (int)rank, (int)world,
+                    cb::peer_exchange_max_ranks());
+    return cuda_result(cb::launch_amax_peer_exchange(local_amax, peer_state, rank, world, out_amax, as_stream(stream)),
+                       name, 1);
+}
+
 int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float* amax, float eps, int32_t code_kind,
                            void* q, float* scale, void* stream) {
     if (!is_float_like(dtype)) return fail(CB_ERR_DTYPE, "cb_cast_per_tensor: bad dtype");

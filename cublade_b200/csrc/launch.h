@@ -57,6 +57,14 @@ cudaError_t launch_cast_tensor(const void* x, int dtype, int64_t n, const float*
 int per_tensor_scratch_floats();
 cudaError_t launch_amax_partials(const void* x, int dtype, int64_t n, float* partials, int* nparts, cudaStream_t s);
 
+// ---- the amax exchange of a sharded per-tensor quantization over peer memory (peer_exchange.cu) ----
+// peer_state[r]: rank r's state array (peer_exchange_state_words() 64-bit words, zeroed once before the first call,
+// mapped into this process); out_amax = max over the ranks' local_amax.  Every rank calls it once per exchange.
+int peer_exchange_state_words();
+int peer_exchange_max_ranks();
+cudaError_t launch_amax_peer_exchange(const float* local_amax, const void* const* peer_state, int rank, int world,
+                                      float* out_amax, cudaStream_t s);
+
 // ---- per-segment (rows of a [nseg, L] matrix: channels or groups), one pass --
 cudaError_t launch_quant_segments(const void* x, int dtype, int64_t nseg, int64_t L, float eps, int code, void* q,
                                   float* scale_out, cudaStream_t s);

@@ -36,19 +36,57 @@ def _native_ops():
     return SimpleNamespace(amax_abs=amax_abs, cast_per_tensor=cast_per_tensor)
 
 
+class PeerAmaxExchange:
+    """The max-exchange of ``quantize_tensor_sharded`` over NVLink peer memory instead of an NCCL call.
+
+    Built once per process group (all ranks on one node, one GPU each): a 264-byte state array per rank in torch's
+    symmetric memory, which maps every rank's array into every process.  ``exchange(local_amax)`` is then one small
+    kernel per rank -- a 64-bit store into each peer's array, a bounded wait on the rank's own -- against tens of
+    microseconds for a 4-byte all-reduce.  Construction is collective (rendezvous + barrier) and raises where
+    symmetric memory is not available; callers fall back to the collective then.
+    """
+
+    def __init__(self, group=None, device: Optional[torch.device] = None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .bindings.cuda.split_phase import peer_exchange_state_bytes
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        words = (peer_exchange_state_bytes() + 7) // 8
+        self.state = symm_mem.empty(words, dtype=torch.int64, device=device)
+        self.state.zero_()
+        self.handle = symm_mem.rendezvous(self.state, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.world:
+            raise RuntimeError("symmetric memory returned a pointer list of another size than the group")
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's array is zero before anybody stores into it
+
+    def exchange(self, local_amax: torch.Tensor) -> torch.Tensor:
+        from .bindings.cuda.split_phase import amax_peer_exchange
+
+        return amax_peer_exchange(local_amax, self.ptrs, self.rank)
+
+
 def quantize_tensor_sharded(x_local: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn, eps: float = 1e-12,
-                            group=None, ops=None) -> QuantizedTensor:
+                            group=None, ops=None, exchange: Optional["PeerAmaxExchange"] = None) -> QuantizedTensor:
     """Per-tensor quantization of a tensor whose rows are spread over the ranks of ``group``.
 
     Every rank passes its own contiguous shard and receives the codes of that shard plus the
-    (identical on all ranks) global scale.  One collective: ``all_reduce(MAX)`` of a float32 scalar.
+    (identical on all ranks) global scale.  One exchange: the maximum of a float32 scalar, by ``all_reduce(MAX)`` or,
+    with ``exchange`` (a ``PeerAmaxExchange`` built for the same group), by peer-memory stores.
     ``ops`` replaces the two kernels (used by CPU tests of the orchestration).
     """
     import torch.distributed as dist
 
     ops = ops or _native_ops()
     amax = ops.amax_abs(x_local)
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+    if exchange is not None:
+        amax = exchange.exchange(amax)
+    elif dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
     q, scale = ops.cast_per_tensor(x_local, amax, dtype, eps)
     zp = torch.zeros((), dtype=torch.float32, device=x_local.device)

@@ -117,6 +117,18 @@ int32_t cb_amax_abs(const void* x, int32_t dtype, int64_t n, float* amax, void* 
 int32_t cb_cast_per_tensor(const void* x, int32_t dtype, int64_t n, const float* amax, float eps, int32_t code_kind,
                            void* q, float* scale, void* stream);
 
+/* The exchange between the two phases over NVLink peer memory instead of a collective call.  No counterpart in the
+ * reference (it has no multi-GPU path).  Every rank owns a state array of cb_peer_exchange_state_bytes() bytes that
+ * all ranks of the node have mapped (CUDA IPC / VMM; zeroed once, followed by a barrier, before the first call) and
+ * passes the mapped addresses of all ranks' arrays, its own included, as peer_state[0..world).  One launch per rank
+ * and exchange: out_amax[0] = max over the ranks of local_amax[0].  The ranks' kernels wait for one another (bounded:
+ * about a second, then NaN is written and the error word of cb_device_error_state is raised), so every rank must be
+ * a process on a GPU of its own; world <= cb_peer_exchange_max_ranks(). */
+int32_t cb_peer_exchange_state_bytes(void);
+int32_t cb_peer_exchange_max_ranks(void);
+int32_t cb_amax_peer_exchange(const float* local_amax, const void* const* peer_state, int32_t rank, int32_t world,
+                              float* out_amax, void* stream);
+
 /* ------------------------------------------------------------------------
  * W8A16 linear:  y[m, n] = (sum_k x[m, k] * wq[n, k]) * scales[n]
  *                          (+ sum_j xo[m, j] * wo[n, j])  (+ bias[n])

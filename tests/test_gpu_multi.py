@@ -3,8 +3,9 @@
 Ranks are child processes, one per GPU, NCCL backend.  Checked: (1) per-tensor FP8 / INT8
 quantization of a row-sharded tensor equals the single-GPU / oracle result bit for bit (one
 float32 max-allreduce is the only exchange); (2) a W8A16 layer sharded over its output features
-reproduces the unsharded layer's output exactly, slice by slice.  Nothing in these tests waits on
-another rank inside a kernel and no rank exits with work in flight."""
+reproduces the unsharded layer's output exactly, slice by slice; (3) the peer-memory form of the exchange
+(one small kernel per rank with a bounded wait on its peers' stores) equals the collective.  No rank exits with
+work in flight."""
 import os
 import socket
 
@@ -59,6 +60,28 @@ def _rank_main(rank, world, port, out):
         n0, n1 = shard_range(1024, rank, world)
         res["w8a16_slice"] = torch.equal(y_mine, y_full[:, n0:n1])
         res["w8a16_gather"] = torch.equal(all_gather_columns(y_mine), y_full)
+        # the same exchange over peer memory (plain peer loads / stores, no multicast): equal to the collective's result
+        # on values that differ per rank and per call, and the sharded quantizer built on it gives the same scale
+        from cublade_b200 import _native as Nat
+        from cublade_b200.sharding import PeerAmaxExchange
+
+        try:
+            ex = PeerAmaxExchange()
+        except Exception as e:  # symmetric memory is not available on every system: the collective stays the route
+            ex, res["peer_exchange_skipped"] = None, True
+        if ex is not None:
+            g = torch.Generator(device="cuda").manual_seed(17 + rank)
+            same = True
+            for i in range(25):
+                a_loc = (torch.rand(1, generator=g, device="cuda") * 10.0 ** (i % 4)).float()
+                want = a_loc.clone()
+                dist.all_reduce(want, op=dist.ReduceOp.MAX)
+                same = same and torch.equal(ex.exchange(a_loc), want)
+            res["peer_exchange_equals_all_reduce"] = same
+            qt_peer = quantize_tensor_sharded(x[a:b].cuda().contiguous(), dtype=torch.float8_e4m3fn, exchange=ex)
+            q_ref, s_ref = O.fp8_quantize(x)
+            res["peer_exchange_fp8_scale"] = qt_peer.scale.cpu().view(torch.int32).item() == s_ref.view(torch.int32).item()
+            res["peer_exchange_no_expired_wait"] = Nat.device_error_state() == 0
         torch.cuda.synchronize()
         dist.barrier()
         out.put((rank, res))

@@ -129,3 +129,68 @@ def test_w8a16_linear_every_path_against_float64(case):
     # the tolerance stated for the layer: relative Frobenius 1e-2, largest deviation 2e-2 of the largest value
     assert rel_fro(y, ref) <= 1e-2
     assert max_abs_ratio(y, ref) <= 2e-2
+
+
+def _w8a8_cases(n, seed):
+    rng = random.Random(seed)
+    return [(i, rng.choice([1, 2, 9, 16, 31, 64, 100, 255, 256, 300, 513]), rng.choice([8, 17, 40, 128, 130, 384, 1000, 2050]),
+             rng.choice([16, 64, 72, 100, 128, 320, 1024, 2064]), rng.choice([torch.bfloat16, torch.float16]), rng.random() < 0.5)
+            for i in range(n)]
+
+
+W8A8_CASES = _w8a8_cases(40, seed=5)
+
+
+@pytest.mark.parametrize("case", W8A8_CASES, ids=[f"{c[0]}-M{c[1]}-N{c[2]}-K{c[3]}-{str(c[4])[6:]}-b{int(c[5])}" for c in W8A8_CASES])
+def test_w8a8_linear_bit_for_bit(case):
+    """Integer tensor cores with exact int32 accumulation: equal to the CPU formulation bit for bit at every shape."""
+    from cublade_b200 import _native as Nat
+    from cublade_b200.bindings.w8a8 import w8a8_linear
+
+    i, M, N, K, dtype, with_bias = case
+    g = torch.Generator().manual_seed(9000 + i)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(dtype)
+    b = torch.randn(N, generator=g).to(dtype) if with_bias else None
+    lay = O.w8a16_quantize(w, dtype)
+    xq, xs = O.int8_quantize_rows(x)
+    y = w8a8_linear(xq.cuda(), xs.cuda(), lay["int8_weights"].cuda(), lay["scales"].cuda(), b.cuda() if with_bias else None,
+                    out_dtype=dtype)
+    assert_bits_equal(y, O.w8a8_forward(x, lay, b, xq=xq, xs=xs), "y")
+    assert Nat.device_error_state() == 0
+
+
+def _gemm_cases(n, seed):
+    rng = random.Random(seed)
+    return [(i, rng.choice([1, 5, 16, 64, 100, 128, 257, 512, 1000]), rng.choice([1, 7, 16, 96, 128, 200, 520, 1024]),
+             rng.choice([1, 9, 16, 64, 100, 128, 1000, 2048]), rng.choice([torch.bfloat16, torch.float16, torch.int8]),
+             rng.choice(["", "leaky_relu"])) for i in range(n)]
+
+
+GEMM_CASES = _gemm_cases(40, seed=6)
+
+
+@pytest.mark.parametrize("case", GEMM_CASES, ids=[f"{c[0]}-M{c[1]}-N{c[2]}-K{c[3]}-{str(c[4])[6:]}-{c[5] or 'none'}" for c in GEMM_CASES])
+def test_generic_matmul_random_shapes(case):
+    """matmul(A, B, activation) (cublade/bindings/triton/matmul.py:17-132) on the tcgen05 GEMM: int8 exact, 16-bit within
+    one rounding of a float64 product."""
+    from cublade_b200 import _native as Nat
+    from cublade_b200.bindings.triton import matmul
+
+    i, M, N, K, dtype, activation = case
+    g = torch.Generator().manual_seed(12000 + i)
+    if dtype == torch.int8:
+        a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+        b = torch.randint(-128, 128, (K, N), generator=g, dtype=torch.int8)
+        got = matmul(a.cuda(), b.cuda(), activation=activation).cpu()
+        assert got.dtype == torch.int32 and torch.equal(got, (a.double() @ b.double()).to(torch.int32))
+    else:
+        a = torch.randn(M, K, generator=g).to(dtype)
+        b = torch.randn(K, N, generator=g).to(dtype)
+        ref = a.double() @ b.double()
+        if activation == "leaky_relu":
+            ref = torch.where(ref >= 0, ref, 0.01 * ref)
+        got = matmul(a.cuda(), b.cuda(), activation=activation).cpu()
+        assert got.dtype == dtype and got.shape == (M, N)
+        assert rel_fro(got, ref) < (3e-3 if dtype == torch.bfloat16 else 5e-4)
+    assert Nat.device_error_state() == 0

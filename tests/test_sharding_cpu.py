@@ -129,3 +129,22 @@ def test_quantize_model_sharded_gives_each_rank_its_rows(monkeypatch):
     assert torch.equal(bias, ref[0].bias)
     assert all(s[2].bias is None and isinstance(s.lm_head, torch.nn.Linear) for s in shards)
     assert shards[1][0].shard == (1, 4, 3, 6)
+
+
+def test_an_exchange_object_replaces_the_collective():
+    """``quantize_tensor_sharded(..., exchange=ex)`` hands the local amax to ``ex.exchange`` (the peer-memory form on
+    GPUs) and does not touch ``torch.distributed``: no process group exists in this test."""
+    from cublade_b200.sharding import quantize_tensor_sharded
+
+    seen = []
+
+    class FakeExchange:
+        def exchange(self, amax):
+            seen.append(float(amax))
+            return torch.maximum(amax, torch.tensor([300.0]))  # as if another rank held the maximum
+
+    x = torch.linspace(-2.0, 2.0, 64).to(torch.bfloat16).reshape(8, 8)
+    qt = quantize_tensor_sharded(x, dtype=torch.int8, ops=_oracle_ops(), exchange=FakeExchange())
+    assert seen == [2.0]
+    assert qt.scale.item() == pytest.approx(300.0 / 127.0, rel=1e-6)
+    assert int(qt.data.abs().max()) == 1  # 2.0 * 127 / 300 rounds to 1: the foreign maximum set the scale

@@ -133,7 +133,13 @@ struct Cfg {
     static constexpr uint32_t n_bars = 3 * kStages + 4;
     static constexpr uint32_t tmem_slot = bars + n_bars * 8;
     static constexpr uint32_t abort_flag = tmem_slot + 4;
-    static constexpr uint32_t total = abort_flag + 4;
+    // Scratch of the epilogue warps for the outlier side product on the warp-level tensor-core path (see the epilogue):
+    // 32 features x 32 activation rows of fp32 per warp, 33 floats per feature so that a lane reading its own feature's
+    // row and its neighbours reading theirs hit 32 different banks.  kSmemA's four 56 KB stages leave no room for it.
+    static constexpr bool kSideMma = MODE != kSmemA;
+    static constexpr uint32_t kSideBytes = 32 * 33 * 4;
+    static constexpr uint32_t side = (abort_flag + 4 + 15u) & ~15u;
+    static constexpr uint32_t total = side + (kSideMma ? kEpiWarps * kSideBytes : 4);
     static constexpr uint32_t kSmemBytes = total + 1024;  // + slack to align the base to 1024 B
     static_assert(kACol + kTmemAStages * kAColsPerStage <= kTmemCols || MODE == kSmemA, "tensor memory map");
     static_assert(kSmemBytes <= 232448, "shared memory map");
@@ -190,6 +196,21 @@ __device__ __forceinline__ bool work_item(const TcParams& p, int num_kb, int idx
 // the input features).  Beyond this bound the call falls back to the streaming kernel.
 constexpr int kMaxKO = 512;
 
+
+// d += a (16 x 16, row-major fragments) . b (16 x 8, column-major fragments), fp32 accumulation, on the warp-level
+// tensor-core path: the outlier side product of a 32 x 32 block of outputs is eight of these instead of ~20 CUDA-core
+// instructions per output.
+template <typename A>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (Widen<A>::kBf16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
 // side += sum over the eight 16-bit pairs of two 16-byte chunks (activation chunk x, weight chunk w), in order
 template <typename A>
@@ -544,10 +565,48 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int side_chunks = p.side_vec ? (int)(p.KO >> 3) : 0;
             const bool side_fast = side_chunks > 0 && side_chunks <= kSideRegs;
             const uint4* wrow4 = reinterpret_cast<const uint4*>(wo + (n_ok ? n : 0) * p.KO);
+            // With room for the scratch (every mode but kSmemA) the side product of a 32 x 32 block runs as eight
+            // mma.m16n8k16: operand A = this warp's 32 outlier-weight rows (two 16-row tiles; fragments fetched once per
+            // work item), operand B = the block's outlier activations (four 8-row tiles), k = the <= 16 outlier columns
+            // (zeros beyond KO).  The products land in the MMA's own layout -- feature 16 i + g (+ 8), row 8 j + 2 t (+ 1)
+            // -- and go through the warp's scratch so that lane l reads the 32 values of ITS feature.  fp32 throughout,
+            // rounded to the activation type where the reference rounds its outlier product.
+            const bool side_mma = C::kSideMma && side_fast;
+            const int g8 = lane >> 2, t4 = lane & 3;
+            uint32_t afr[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
             uint4 wreg[kSideRegs];
+            if (side_mma) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int64_t n_lo = (int64_t)tn * kTileN + quarter * 32 + 16 * i + g8, n_hi = n_lo + 8;
+                    const uint32_t* r_lo = reinterpret_cast<const uint32_t*>(wo + (n_lo < p.N ? n_lo : p.N - 1) * p.KO);
+                    const uint32_t* r_hi = reinterpret_cast<const uint32_t*>(wo + (n_hi < p.N ? n_hi : p.N - 1) * p.KO);
+                    afr[i][0] = __ldg(r_lo + t4);
+                    afr[i][1] = __ldg(r_hi + t4);
+                    if (side_chunks > 1) {
+                        afr[i][2] = __ldg(r_lo + 4 + t4);
+                        afr[i][3] = __ldg(r_hi + 4 + t4);
+                    }
+                }
+            }
 #pragma unroll
             for (int ch = 0; ch < kSideRegs; ++ch)
-                wreg[ch] = (n_ok && ch < side_chunks) ? __ldg(wrow4 + ch) : make_uint4(0u, 0u, 0u, 0u);
+                wreg[ch] = (!side_mma && n_ok && ch < side_chunks) ? __ldg(wrow4 + ch) : make_uint4(0u, 0u, 0u, 0u);
+            // Operand-B fragments (outlier activations) of a 32-row block are fetched one block ahead -- the first block's
+            // before the wait for the accumulator, a tile's first block's during the last block of the tile before -- so
+            // that their trip to L2 runs under other work: issued inside their own block, as they were at first, every
+            // block stalled on them (M = 2048: 13 blocks per work item, +26 us).
+            auto load_bfr = [&](int64_t mb, int c0, uint32_t (&b)[4][2]) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t mr = mb + c0 + 8 * j + g8;
+                    const uint32_t* xr32 = reinterpret_cast<const uint32_t*>(xo + (mr < p.M ? mr : p.M - 1) * p.ldxo);
+                    b[j][0] = __ldg(xr32 + t4);
+                    b[j][1] = side_chunks > 1 ? __ldg(xr32 + 4 + t4) : 0u;
+                }
+            };
+            uint32_t bnext[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
+            if (side_mma) load_bfr((int64_t)tx * C::kHalves * p.tile_x, 0, bnext);
             {
                 int okw = 1;
                 if (lane == 0) {
@@ -587,8 +646,18 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
                 // this block's outlier activations: row c0 + lane, one 16-byte chunk per register (rows beyond M re-read
                 // row M - 1); issued before the wait so that the loads fly with the tensor-memory load
+                uint32_t bfr[4][2];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    bfr[j][0] = bnext[j][0];
+                    bfr[j][1] = bnext[j][1];
+                }
+                if (side_mma) {
+                    if (c0 + 32 < p.tile_x && m_base + c0 + 32 < p.M) load_bfr(m_base, c0 + 32, bnext);
+                    else if (half + 1 < C::kHalves && m_base + p.tile_x < p.M) load_bfr(m_base + p.tile_x, 0, bnext);
+                }
                 uint4 xblk[kSideRegs];
-                if (side_fast) {
+                if (side_fast && !side_mma) {
                     const int64_t mr = m_base + c0 + lane;
                     const uint4* xr = reinterpret_cast<const uint4*>(xo + (mr < p.M ? mr : p.M - 1) * p.ldxo);
 #pragma unroll
@@ -617,6 +686,35 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         v = has_bias ? Widen<A>::add2(v, bias2) : v;
                         if (n_ok && c < nrows) yrow[(int64_t)c * ystep] = (uint16_t)(v & 0xffffu);
                         if (n_ok && c + 1 < nrows) yrow[(int64_t)(c + 1) * ystep] = (uint16_t)(v >> 16);
+                    }
+                    continue;
+                }
+                if (side_mma) {
+                    if constexpr (C::kSideMma) {
+                        float* scratch = reinterpret_cast<float*>(gbase + C::side) + (warp - 2) * (32 * 33);
+#pragma unroll
+                        for (int i = 0; i < 2; ++i)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                                mma16816<A>(d, afr[i], bfr[j][0], bfr[j][1]);
+                                float* dst = scratch + (16 * i + g8) * 33 + 8 * j + 2 * t4;
+                                dst[0] = d[0];
+                                dst[1] = d[1];
+                                dst[8 * 33] = d[2];
+                                dst[8 * 33 + 1] = d[3];
+                            }
+                        __syncwarp();
+                        const float* mine = scratch + lane * 33;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            uint32_t v = Widen<A>::mul2(Widen<A>::pack2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2);
+                            v = Widen<A>::add2(v, Widen<A>::pack2(mine[c], mine[c + 1]));
+                            v = has_bias ? Widen<A>::add2(v, bias2) : v;
+                            if (n_ok && c < nrows) yrow[(int64_t)c * ystep] = (uint16_t)(v & 0xffffu);
+                            if (n_ok && c + 1 < nrows) yrow[(int64_t)(c + 1) * ystep] = (uint16_t)(v >> 16);
+                        }
+                        __syncwarp();  // the scratch is rewritten by the next block
                     }
                     continue;
                 }
